@@ -1,0 +1,81 @@
+// Shared declarations of the kernel library: dtype codes, status codes, the last-error
+// string, and small device helpers.  Every entry point is `extern "C"`, takes raw device
+// pointers and a stream, validates its arguments on the host before any launch and returns a
+// status; nothing here allocates device memory.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+enum SbDtype { SB_F32 = 0, SB_BF16 = 1 };
+enum SbStatus { SB_OK = 0, SB_ERR_ARG = 1, SB_ERR_UNSUPPORTED = 2, SB_ERR_CUDA = 3 };
+enum SbEpilogue { SB_EPI_NONE = 0, SB_EPI_BIAS = 1, SB_EPI_RESIDUAL = 2, SB_EPI_SWIGLU = 3 };
+
+// Rows of a fused gate/up matrix alternate in blocks of this many: 8 gate rows, then the 8 up
+// rows of the same outputs.  Every GEMM kernel's SwiGLU epilogue pairs column c with c + 8.
+#define SB_SWIGLU_BLOCK 8
+
+extern "C" const char* sb_last_error();
+void sb_set_error(const char* fmt, ...);
+
+#define SB_FAIL(code, ...)        \
+  do {                            \
+    sb_set_error(__VA_ARGS__);    \
+    return (code);                \
+  } while (0)
+
+#define SB_CHECK_LAUNCH(name)                                                      \
+  do {                                                                             \
+    cudaError_t e__ = cudaGetLastError();                                          \
+    if (e__ != cudaSuccess)                                                        \
+      SB_FAIL(SB_ERR_CUDA, "%s: launch failed: %s", name, cudaGetErrorString(e__)); \
+  } while (0)
+
+template <typename T>
+__device__ __forceinline__ float sb_to_f32(T v);
+template <>
+__device__ __forceinline__ float sb_to_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float sb_to_f32<__nv_bfloat16>(__nv_bfloat16 v) {
+  return __bfloat162float(v);
+}
+
+template <typename T>
+__device__ __forceinline__ T sb_from_f32(float v);
+template <>
+__device__ __forceinline__ float sb_from_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 sb_from_f32<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+
+// x / (1 + exp(-x)) with the accurate expf, as the reference's silu
+// (core/src/nn/activation.cpp:41-50, core/src/nn/cuda_elementwise.cu:203-212).
+__device__ __forceinline__ float sb_silu(float x) { return x / (1.0f + expf(-x)); }
+
+__device__ __forceinline__ float sb_warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float sb_warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Dispatch helpers: run `BODY` with `T` bound to the C++ type of a dtype code.
+#define SB_DISPATCH_DTYPE(code, T, ...)                           \
+  do {                                                            \
+    if ((code) == SB_F32) {                                       \
+      using T = float;                                            \
+      __VA_ARGS__                                                 \
+    } else {                                                      \
+      using T = __nv_bfloat16;                                    \
+      __VA_ARGS__                                                 \
+    }                                                             \
+  } while (0)
+
+static inline bool sb_valid_dtype(int d) { return d == SB_F32 || d == SB_BF16; }

@@ -1,0 +1,193 @@
+// Embedding gather, RMSNorm, dtype casts and the fused rotation + cache write.
+// Each kernel is templated on its storage types; arithmetic is float32 throughout.
+#include <stdarg.h>
+
+#include "common.cuh"
+
+static thread_local char g_error[512] = "";
+
+extern "C" const char* sb_last_error() { return g_error; }
+
+void sb_set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+}
+
+extern "C" int sb_abi_version() { return 1; }
+
+// ------------------------------------------------------------------------------- embedding
+// x[t, :] = E[tokens[t], :] as float32; no sqrt(width) scale for this architecture
+// (core/src/model/emit.cpp:237-247, core/src/nn/embedding.cpp:23-28).
+template <typename TW>
+__global__ void embed_kernel(const int32_t* __restrict__ tokens, const TW* __restrict__ table,
+                             int width, float* __restrict__ out) {
+  const int t = blockIdx.x;
+  const TW* row = table + (size_t)tokens[t] * width;
+  float* o = out + (size_t)t * width;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = sb_to_f32<TW>(row[i]);
+}
+
+extern "C" int sb_embed(const int32_t* tokens, int n_rows, const void* table, int table_dtype,
+                        int width, float* out, cudaStream_t stream) {
+  if (n_rows <= 0 || width <= 0) SB_FAIL(SB_ERR_ARG, "sb_embed: n_rows=%d width=%d", n_rows, width);
+  if (!sb_valid_dtype(table_dtype)) SB_FAIL(SB_ERR_ARG, "sb_embed: table dtype %d", table_dtype);
+  SB_DISPATCH_DTYPE(table_dtype, TW, {
+    embed_kernel<TW><<<n_rows, 256, 0, stream>>>(tokens, (const TW*)table, width, out);
+  });
+  SB_CHECK_LAUNCH("sb_embed");
+  return SB_OK;
+}
+
+// --------------------------------------------------------------------------------- RMSNorm
+// inv = 1/sqrt(mean(x^2) + eps); y = (x * inv) * w, plain weight
+// (core/src/nn/norm.cpp:25-42, core/src/nn/cuda_elementwise.cu:684-711).  One block per row;
+// the sum is a fixed tree (thread-strided partial sums, warp shuffles, then the warps in
+// order), so a row's result does not depend on which other rows are in the launch.
+// `rows`, when given, gathers: output row r is the norm of input row rows[r].
+template <typename TW, typename TO>
+__global__ void rmsnorm_kernel(const float* __restrict__ x, const int32_t* __restrict__ rows,
+                               const TW* __restrict__ w, int width, float eps,
+                               TO* __restrict__ out) {
+  __shared__ float warp_sums[32];
+  __shared__ float inv_shared;
+  const int r = blockIdx.x;
+  const float* xr = x + (size_t)(rows ? rows[r] : r) * width;
+  float s = 0.0f;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    const float v = xr[i];
+    s = fmaf(v, v, s);
+  }
+  s = sb_warp_sum(s);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+  if (lane == 0) warp_sums[warp] = s;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float total = 0.0f;
+    for (int i = 0; i < n_warps; ++i) total += warp_sums[i];
+    inv_shared = 1.0f / sqrtf(total / (float)width + eps);
+  }
+  __syncthreads();
+  const float inv = inv_shared;
+  TO* o = out + (size_t)r * width;
+  for (int i = threadIdx.x; i < width; i += blockDim.x)
+    o[i] = sb_from_f32<TO>((xr[i] * inv) * sb_to_f32<TW>(w[i]));
+}
+
+extern "C" int sb_rmsnorm(const float* x, const int32_t* rows, int n_rows, int width,
+                          const void* weight, int weight_dtype, float eps, void* out,
+                          int out_dtype, cudaStream_t stream) {
+  if (n_rows <= 0 || width <= 0) SB_FAIL(SB_ERR_ARG, "sb_rmsnorm: n_rows=%d width=%d", n_rows, width);
+  if (!sb_valid_dtype(weight_dtype) || !sb_valid_dtype(out_dtype))
+    SB_FAIL(SB_ERR_ARG, "sb_rmsnorm: dtype codes %d %d", weight_dtype, out_dtype);
+  if (!(eps >= 0.0f)) SB_FAIL(SB_ERR_ARG, "sb_rmsnorm: eps %g", eps);
+  const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+  SB_DISPATCH_DTYPE(weight_dtype, TW, {
+    SB_DISPATCH_DTYPE(out_dtype, TO, {
+      rmsnorm_kernel<TW, TO><<<n_rows, threads, 0, stream>>>(x, rows, (const TW*)weight, width,
+                                                             eps, (TO*)out);
+    });
+  });
+  SB_CHECK_LAUNCH("sb_rmsnorm");
+  return SB_OK;
+}
+
+// ------------------------------------------------------------------------------------ cast
+template <typename TI, typename TO>
+__global__ void cast_kernel(const TI* __restrict__ in, TO* __restrict__ out, size_t n) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (size_t)gridDim.x * blockDim.x)
+    out[i] = sb_from_f32<TO>(sb_to_f32<TI>(in[i]));
+}
+
+extern "C" int sb_cast(const void* in, int in_dtype, void* out, int out_dtype, size_t n,
+                       cudaStream_t stream) {
+  if (!sb_valid_dtype(in_dtype) || !sb_valid_dtype(out_dtype))
+    SB_FAIL(SB_ERR_ARG, "sb_cast: dtype codes %d %d", in_dtype, out_dtype);
+  if (n == 0) return SB_OK;
+  const int blocks = (int)((n + 255) / 256 < 4096 ? (n + 255) / 256 : 4096);
+  SB_DISPATCH_DTYPE(in_dtype, TI, {
+    SB_DISPATCH_DTYPE(out_dtype, TO, {
+      cast_kernel<TI, TO><<<blocks, 256, 0, stream>>>((const TI*)in, (TO*)out, n);
+    });
+  });
+  SB_CHECK_LAUNCH("sb_cast");
+  return SB_OK;
+}
+
+// ------------------------------------------------------------- rotation + cache write
+// Input: the fused projection row [q heads | k heads | v heads] in float32 (bias already added).
+// Half-split rotation of the first `rot` dims of each q and k head: for i < rot/2,
+// theta = float(pos) * inv_freq[i]; x'_i = x_i c - x_{i+rot/2} s; x'_{i+rot/2} = x_i s +
+// x_{i+rot/2} c, in float32 with the accurate sinf/cosf (core/src/nn/rope.cpp:26-82,
+// core/src/nn/cuda_elementwise.cu:326-347).  Rotated q goes to q_out [row, head, hd]; rotated k
+// and v go to the sequence's cache page of that position (core/src/model/emit.cpp:291-293,
+// core/src/nn/cuda_elementwise.cu:2639), rounded only to the cache's own dtype.
+//
+// Cache of one schedule entry: [page][k|v][kv head][slot in page][hd].  The page of position p
+// of sequence b is page_ids[page_off[b] + p / page_size].
+template <typename TQ, typename TC>
+__global__ void rope_store_kernel(const float* __restrict__ qkv, int n_q_heads, int n_kv_heads,
+                                  int hd, int rot, const float* __restrict__ inv_freq,
+                                  const int32_t* __restrict__ row_seq,
+                                  const int32_t* __restrict__ row_pos,
+                                  const int32_t* __restrict__ page_off,
+                                  const int32_t* __restrict__ page_ids, int page_size,
+                                  TC* __restrict__ cache, TQ* __restrict__ q_out, int has_kv) {
+  const int t = blockIdx.x;
+  const int head = blockIdx.y;                       // q heads, then k heads, then v heads
+  const int width_in = (n_q_heads + (has_kv ? 2 * n_kv_heads : 0)) * hd;
+  const float* src = qkv + (size_t)t * width_in + (size_t)head * hd;
+  const int pos = row_pos[t];
+  const int half = rot >> 1;
+  const bool is_v = head >= n_q_heads + n_kv_heads;
+
+  for (int e = threadIdx.x; e < hd; e += blockDim.x) {
+    float v = src[e];
+    if (!is_v && e < rot) {
+      const int i = e < half ? e : e - half;
+      const float theta = (float)pos * inv_freq[i];
+      const float c = cosf(theta), s = sinf(theta);
+      v = e < half ? src[e] * c - src[e + half] * s : src[e - half] * s + src[e] * c;
+    }
+    if (head < n_q_heads) {
+      q_out[((size_t)t * n_q_heads + head) * hd + e] = sb_from_f32<TQ>(v);
+    } else {
+      const int b = row_seq[t];
+      const int page = page_ids[page_off[b] + pos / page_size];
+      const int kvh = is_v ? head - n_q_heads - n_kv_heads : head - n_q_heads;
+      const size_t off =
+          ((((size_t)page * 2 + (is_v ? 1 : 0)) * n_kv_heads + kvh) * page_size + pos % page_size) *
+              hd + e;
+      cache[off] = sb_from_f32<TC>(v);
+    }
+  }
+}
+
+extern "C" int sb_rope_store(const float* qkv, int n_rows, int n_q_heads, int n_kv_heads, int hd,
+                             int rot, const float* inv_freq, const int32_t* row_seq,
+                             const int32_t* row_pos, const int32_t* page_off,
+                             const int32_t* page_ids, int page_size, void* cache, int cache_dtype,
+                             void* q_out, int q_dtype, int has_kv, cudaStream_t stream) {
+  if (n_rows <= 0 || n_q_heads <= 0 || hd <= 0 || (has_kv && n_kv_heads <= 0))
+    SB_FAIL(SB_ERR_ARG, "sb_rope_store: n_rows=%d heads=%d/%d hd=%d", n_rows, n_q_heads,
+            n_kv_heads, hd);
+  if (rot < 0 || rot > hd || (rot & 1))
+    SB_FAIL(SB_ERR_ARG, "sb_rope_store: rotary dims %d of head dim %d (must be even, <= hd)", rot, hd);
+  if (!sb_valid_dtype(cache_dtype) || !sb_valid_dtype(q_dtype))
+    SB_FAIL(SB_ERR_ARG, "sb_rope_store: dtype codes %d %d", cache_dtype, q_dtype);
+  if (has_kv && (page_size <= 0 || !cache || !page_off || !page_ids))
+    SB_FAIL(SB_ERR_ARG, "sb_rope_store: cache arguments missing");
+  const dim3 grid(n_rows, n_q_heads + (has_kv ? 2 * n_kv_heads : 0));
+  const int threads = hd >= 128 ? 128 : (hd >= 64 ? 64 : 32);
+  SB_DISPATCH_DTYPE(q_dtype, TQ, {
+    SB_DISPATCH_DTYPE(cache_dtype, TC, {
+      rope_store_kernel<TQ, TC><<<grid, threads, 0, stream>>>(
+          qkv, n_q_heads, n_kv_heads, hd, rot, inv_freq, row_seq, row_pos, page_off, page_ids,
+          page_size, (TC*)cache, (TQ*)q_out, has_kv);
+    });
+  });
+  SB_CHECK_LAUNCH("sb_rope_store");
+  return SB_OK;
+}

@@ -1,0 +1,36 @@
+"""An engine: one bound model, its cache, and the step function over them."""
+from __future__ import annotations
+
+import torch
+
+from ..cache.kv import Cache
+from .step import StepEntry, step
+
+
+class Engine:
+    """Owns the cache of a model and runs steps on it.
+
+    `max_tokens` is the most tokens live sequences may hold together, each sequence's count
+    rounded up to a whole cache page (64 tokens); it sizes the cache."""
+
+    def __init__(self, model, max_tokens: int, n_slots: int | None = None):
+        self.model = model
+        self.cache = Cache(model.kv_needs(), model.state_needs(), max_tokens,
+                           dtype=model.dtype, device=model.device, n_slots=n_slots)
+
+    def open(self) -> int:
+        """A slot for a new sequence."""
+        return self.cache.open()
+
+    def close(self, slot: int) -> None:
+        """Gives the sequence's slot and pages back."""
+        self.cache.close(slot)
+
+    def length(self, slot: int) -> int:
+        return self.cache.length(slot)
+
+    def step(self, entries) -> torch.Tensor:
+        """entries: StepEntry items or (slot, tokens, want) tuples."""
+        entries = [e if isinstance(e, StepEntry) else StepEntry(e[0], list(e[1]), list(e[2]))
+                   for e in entries]
+        return step(self.model, self.cache, entries)

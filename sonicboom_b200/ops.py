@@ -1,0 +1,209 @@
+"""Python face of the kernel library: each function checks its tensors, then calls one
+`extern "C"` entry point on torch's current CUDA stream.
+
+Nothing here computes with torch; a tensor that is not on a CUDA device, or a missing
+library, is an error (there is no CPU path).  Shapes a kernel does not take are refused by
+the kernel's own host-side checks, whose message is raised here.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from .csrc import build as _build
+
+F32, BF16 = 0, 1
+EPI_NONE, EPI_BIAS, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2, 3
+SWIGLU_BLOCK = 8                 # rows of gate and up alternate in blocks of this many
+SKINNY_MAX_ROWS = 64             # bfloat16 products of at most this many rows stream the weights
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_lib = None
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        l = _build.load()
+        l.sb_last_error.restype = ctypes.c_char_p
+        _lib = l
+    return _lib
+
+
+def _code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return F32
+    if dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"kernels take float32 and bfloat16 tensors, not {dtype}")
+
+
+def _ptr(t):
+    if t is None:
+        return ctypes.c_void_p(0)
+    if not t.is_cuda:
+        raise KernelError("kernels take CUDA tensors only; there is no CPU path")
+    if not t.is_contiguous():
+        raise KernelError("kernels take contiguous tensors")
+    return ctypes.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise KernelError(f"{what}: {lib().sb_last_error().decode()}")
+
+
+def _i32(t, what):
+    if t.dtype != torch.int32:
+        raise KernelError(f"{what} must be int32, got {t.dtype}")
+    return _ptr(t)
+
+
+def embed(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[t] = table[tokens[t]] as float32."""
+    n, width = tokens.numel(), table.shape[1]
+    assert out.dtype == torch.float32 and out.shape == (n, width)
+    _check(lib().sb_embed(_i32(tokens, "tokens"), n, _ptr(table), _code(table.dtype), width,
+                          _ptr(out), _stream()), "embed")
+    return out
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
+            rows: torch.Tensor | None = None) -> torch.Tensor:
+    """out[r] = rmsnorm(x[rows[r]] or x[r]) * weight; x is the float32 residual stream."""
+    assert x.dtype == torch.float32 and x.dim() == 2
+    n = out.shape[0]
+    width = x.shape[1]
+    assert out.shape[1] == width and weight.numel() == width
+    if rows is None:
+        assert x.shape[0] == n
+    _check(lib().sb_rmsnorm(_ptr(x), _i32(rows, "rows") if rows is not None else _ptr(None), n,
+                            width, _ptr(weight), _code(weight.dtype), ctypes.c_float(eps),
+                            _ptr(out), _code(out.dtype), _stream()), "rmsnorm")
+    return out
+
+
+def cast(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    if x.dtype == dtype:
+        return x
+    out = torch.empty_like(x, dtype=dtype)
+    _check(lib().sb_cast(_ptr(x), _code(x.dtype), _ptr(out), _code(dtype),
+                         ctypes.c_size_t(x.numel()), _stream()), "cast")
+    return out
+
+
+def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = EPI_NONE,
+           bias: torch.Tensor | None = None, residual: torch.Tensor | None = None,
+           kernel: str = "auto") -> torch.Tensor:
+    """out = a @ w.T with a fused epilogue; a [M,K], w [N,K]; float32 accumulation.
+
+    bfloat16 operands run on tensor cores (weight-streaming kernel up to SKINNY_MAX_ROWS rows,
+    tiled kernel above); float32 operands run on the plain FFMA kernel, which is also what
+    `kernel="plain"` forces for any dtypes.  Mixed operand dtypes are cast to float32 first.
+    """
+    M, K = a.shape
+    N = w.shape[0]
+    assert w.shape[1] == K, f"linear: a is [{M},{K}], w is {tuple(w.shape)}"
+    n_out = N // 2 if epilogue == EPI_SWIGLU else N
+    assert tuple(out.shape) == (M, n_out), f"linear: out is {tuple(out.shape)}, want {(M, n_out)}"
+    if a.dtype != w.dtype:
+        a = cast(a, torch.float32)
+        if w.dtype != torch.float32:
+            raise KernelError("linear: a float32 activation needs float32 weights")
+    args = (_ptr(a), _code(a.dtype), _ptr(w), _code(w.dtype), M, N, K, epilogue, _ptr(bias),
+            _code(bias.dtype) if bias is not None else 0, _ptr(residual), _ptr(out),
+            _code(out.dtype), _stream())
+    if residual is not None:
+        assert residual.dtype == torch.float32 and tuple(residual.shape) == (M, N)
+    if bias is not None:
+        assert bias.numel() == N
+    fast = a.dtype == torch.bfloat16 and kernel != "plain"
+    l = lib()
+    if fast and (kernel == "skinny" or (kernel == "auto" and M <= SKINNY_MAX_ROWS)) \
+            and hasattr(l, "sb_gemm_skinny"):
+        _check(l.sb_gemm_skinny(*args), "linear (weight-streaming kernel)")
+    elif fast and hasattr(l, "sb_gemm_tiled"):
+        _check(l.sb_gemm_tiled(*args), "linear (tiled kernel)")
+    else:
+        _check(l.sb_gemm_plain(*args), "linear (plain kernel)")
+    return out
+
+
+def rope_store(qkv: torch.Tensor, n_q_heads: int, n_kv_heads: int, head_dim: int, rotary_dim: int,
+               inv_freq: torch.Tensor, row_seq, row_pos, page_off, page_ids, page_size: int,
+               cache: torch.Tensor | None, q_out: torch.Tensor) -> torch.Tensor:
+    """Rotates q and k, writes q to q_out [rows, heads, hd] and k, v into the cache pages.
+    With cache=None the input row holds queries only (a layer that reads another's cache)."""
+    n = qkv.shape[0]
+    has_kv = cache is not None
+    assert qkv.dtype == torch.float32
+    assert qkv.shape[1] == (n_q_heads + (2 * n_kv_heads if has_kv else 0)) * head_dim
+    assert inv_freq.dtype == torch.float32 and inv_freq.numel() >= rotary_dim // 2
+    _check(lib().sb_rope_store(
+        _ptr(qkv), n, n_q_heads, n_kv_heads, head_dim, rotary_dim, _ptr(inv_freq),
+        _i32(row_seq, "row_seq"), _i32(row_pos, "row_pos"),
+        _i32(page_off, "page_off") if has_kv else _ptr(None),
+        _i32(page_ids, "page_ids") if has_kv else _ptr(None), page_size,
+        _ptr(cache), _code(cache.dtype) if has_kv else _code(q_out.dtype), _ptr(q_out),
+        _code(q_out.dtype), 1 if has_kv else 0, _stream()), "rope_store")
+    return q_out
+
+
+def attention(q: torch.Tensor, out: torch.Tensor, plan, group_index: int, cache: torch.Tensor,
+              n_q_heads: int, n_kv_heads: int, head_dim: int, window: int, scale: float,
+              kernel: str = "auto") -> torch.Tensor:
+    """Causal grouped-query attention of the step's rows over one cache entry's pages."""
+    n = q.shape[0]
+    g = plan.groups[group_index]
+    l = lib()
+    fast = q.dtype == torch.bfloat16 and kernel != "plain" and hasattr(l, "sb_attention")
+    if fast:
+        _check(l.sb_attention(
+            _ptr(q), _ptr(out), n, plan.n_seqs, plan.max_new, _i32(plan.seq_row0, "seq_row0"),
+            _i32(plan.seq_pos0, "seq_pos0"), _i32(g.page_off, "page_off"),
+            _i32(g.page_ids, "page_ids"), g.page_size, _ptr(cache), n_q_heads, n_kv_heads,
+            head_dim, window, ctypes.c_float(scale), _ptr(plan.attn_scratch(q.device)),
+            ctypes.c_size_t(plan.attn_scratch_bytes), plan.max_len, _stream()), "attention")
+    else:
+        _check(l.sb_attention_plain(
+            _ptr(q), _ptr(out), _code(q.dtype), n, _i32(plan.row_seq, "row_seq"),
+            _i32(plan.row_pos, "row_pos"), _i32(g.page_off, "page_off"),
+            _i32(g.page_ids, "page_ids"), g.page_size, _ptr(cache), _code(cache.dtype),
+            n_q_heads, n_kv_heads, head_dim, window, ctypes.c_float(scale), _stream()),
+            "attention (plain kernel)")
+    return out
+
+
+def sample_params_size() -> int:
+    return lib().sb_sample_params_size()
+
+
+def sample(logits: torch.Tensor, params: torch.Tensor, history: torch.Tensor | None,
+           out_tokens: torch.Tensor) -> torch.Tensor:
+    """One token per logits row; `params` is a uint8 tensor of packed per-row records."""
+    n, vocab = logits.shape
+    assert logits.dtype == torch.float32 and params.dtype == torch.uint8
+    assert params.numel() == n * sample_params_size()
+    stride = history.shape[1] if history is not None else 0
+    _check(lib().sb_sample(_ptr(logits), n, vocab, _ptr(params),
+                           _i32(history, "history") if history is not None else _ptr(None),
+                           stride, _i32(out_tokens, "out_tokens"), _stream()), "sample")
+    return out_tokens
+
+
+def attention_scratch_bytes(plan) -> int:
+    """Bytes of scratch the split attention kernel needs for this step's batch."""
+    l = lib()
+    if not hasattr(l, "sb_attention_scratch_bytes"):
+        return 0
+    l.sb_attention_scratch_bytes.restype = ctypes.c_size_t
+    return int(l.sb_attention_scratch_bytes(plan.n_seqs, plan.max_new, plan.max_len))

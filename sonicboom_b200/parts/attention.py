@@ -1,0 +1,86 @@
+"""Grouped-query attention over the paged cache, the mixer of this architecture.
+
+Order of operations as the reference's emitter writes it (core/src/model/emit.cpp:255-308):
+q = Wq h + bq; rotate q; k = Wk h, v = Wv h, then their biases; rotate k; store k, v; attend
+with scale applied after the dot and a causal (optionally windowed) mask
+(core/src/nn/attention.cpp:26-105); output projection without bias; the residual add is
+fused into that projection.  The three input projections are one product over a fused
+[q | k | v] matrix, the way the reference reads "sibling" weights in one launch
+(core/src/quant/mmvq_q8_1.cuh:634).  An entry that reads another entry's cache projects
+queries only."""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..cache.kv import KVNeed
+from ..weights.loader import TensorRequest
+from .base import POSITION_ENCODINGS, Mixer, make, register_mixer
+
+
+@register_mixer("attention")
+class Attention(Mixer):
+    def __init__(self, spec, dtype, device):
+        self.spec, self.dtype, self.device = spec, dtype, device
+        self.hq, self.hkv, self.hd = spec.n_heads, spec.n_kv_heads, spec.head_dim
+        self.qw, self.kvw = self.hq * self.hd, self.hkv * self.hd
+        if spec.out_bias:
+            from ..config.specs import ConfigError
+            raise ConfigError("attention with an output-projection bias is not built")
+        if self.hq % self.hkv:
+            from ..config.specs import ConfigError
+            raise ConfigError(f"{self.hq} query heads are not a multiple of {self.hkv} key/value heads")
+        self.position = make(POSITION_ENCODINGS, "position encoding", spec.position, dtype, device)
+        self.w_qkv = self.b_qkv = self.w_o = None
+
+    def kv_need(self):
+        return KVNeed(self.hkv, self.hd, self.spec.window)
+
+    def tensor_requests(self):
+        p, d = self.spec.prefix, self.spec.width
+        req = [TensorRequest(p + "q_proj.weight", (self.qw, d)),
+               TensorRequest(p + "k_proj.weight", (self.kvw, d)),
+               TensorRequest(p + "v_proj.weight", (self.kvw, d)),
+               TensorRequest(p + "o_proj.weight", (d, self.qw))]
+        if self.spec.qkv_bias:
+            req += [TensorRequest(p + "q_proj.bias", (self.qw,), "bias"),
+                    TensorRequest(p + "k_proj.bias", (self.kvw,), "bias"),
+                    TensorRequest(p + "v_proj.bias", (self.kvw,), "bias")]
+        return req
+
+    def bind(self, get):
+        p = self.spec.prefix
+        self.w_qkv = _cat([get(p + f"{n}_proj.weight") for n in "qkv"])
+        if self.spec.qkv_bias:
+            self.b_qkv = _cat([get(p + f"{n}_proj.bias") for n in "qkv"])
+        self.w_o = get(p + "o_proj.weight")
+
+    def forward(self, h, ctx, residual=None):
+        rows = h.shape[0]
+        plan = ctx.plan
+        width_in = self.qw + (2 * self.kvw if ctx.owns_cache else 0)
+        qkv = torch.empty((rows, width_in), dtype=torch.float32, device=h.device)
+        ops.linear(h, self.w_qkv[:width_in], qkv,
+                   ops.EPI_BIAS if self.b_qkv is not None else ops.EPI_NONE,
+                   bias=self.b_qkv[:width_in] if self.b_qkv is not None else None)
+        storage = ctx.kv_storage()
+        g = plan.groups[ctx.kv_group()]
+        q = torch.empty((rows, self.hq, self.hd), dtype=self.dtype, device=h.device)
+        ops.rope_store(qkv, self.hq, self.hkv, self.hd, self.position.rotary_dim,
+                       self.position.inv_freq, plan.row_seq, plan.row_pos, g.page_off, g.page_ids,
+                       g.page_size, storage if ctx.owns_cache else None, q)
+        mixed = torch.empty((rows, self.qw), dtype=self.dtype, device=h.device)
+        ops.attention(q, mixed, plan, ctx.kv_group(), storage, self.hq, self.hkv, self.hd,
+                      self.spec.window, self.spec.scale)
+        out = residual if residual is not None else \
+            torch.empty((rows, self.spec.width), dtype=torch.float32, device=h.device)
+        return ops.linear(mixed, self.w_o, out,
+                          ops.EPI_RESIDUAL if residual is not None else ops.EPI_NONE,
+                          residual=residual)
+
+
+def _cat(tensors):
+    """Rows of several tensors in one; a mix of kept dtypes goes to the widest."""
+    if len({t.dtype for t in tensors}) > 1:
+        tensors = [t.float() for t in tensors]
+    return torch.cat(tensors, dim=0).contiguous()

@@ -1,0 +1,133 @@
+"""Interfaces of the parts a layer is put together from, and the registries that name them.
+
+A part knows its own sizes and constants (they come in through its spec record) and nothing
+about the model it sits in.  The configuration chooses parts layer by layer through the
+`kind` strings of the spec records; `register_*` adds a kind without touching this package.
+
+Every part follows the same life cycle:
+    part = Kind(spec, dtype, device)      # sizes and constants only
+    part.tensor_requests()                # which tensors it wants, by name and shape
+    part.bind(get)                        # get(name) -> device tensor; fuse / lay out weights
+    part.forward(...)                     # run on the rows of one step
+
+What a step hands to parts is a `StepContext`: the step's device-side plan (rows, positions,
+page tables), the cache, and which schedule entry is running.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Callable, Optional
+
+import torch
+
+from ..cache.kv import Cache, KVNeed, StateNeed
+from ..weights.loader import TensorRequest
+
+
+@dataclass
+class StepContext:
+    plan: object                   # engine.step.StepPlan
+    cache: Cache
+    entry: int = 0                 # index of the running schedule entry
+    kv_entry: int = 0              # entry whose cache is read (== entry when it owns one)
+    owns_cache: bool = True
+
+    def kv_storage(self) -> torch.Tensor:
+        """[page, k|v, kv head, position in page, hd] of the cache this entry reads."""
+        g = self.cache.groups[self.cache.group_of_entry[self.kv_entry]]
+        return g.entry_storage(self.kv_entry)
+
+    def kv_group(self) -> int:
+        return self.cache.group_of_entry[self.kv_entry]
+
+    def state(self) -> torch.Tensor:
+        """[slot, ...] state tensor of the running entry; rows are `plan.seq_slot`."""
+        return self.cache.state[self.entry]
+
+
+class Part:
+    def tensor_requests(self) -> list[TensorRequest]:
+        return []
+
+    def bind(self, get: Callable[[str], torch.Tensor]) -> None:
+        pass
+
+
+class Norm(Part):
+    """forward(x float32 [rows, width], out_dtype, rows=None) -> [n, width] in out_dtype;
+    with `rows` (device int32) only those rows of x are normed, in that order."""
+
+    def forward(self, x, out_dtype, rows=None):
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    """Supplies what the rotation kernel consumes: `rotary_dim` and a float32 table
+    `inv_freq[rotary_dim/2]` on the device (angle = position * inv_freq[i])."""
+    rotary_dim: int = 0
+    inv_freq: Optional[torch.Tensor] = None
+
+
+class Mixer(Part):
+    """forward(h [rows, width] in the activation dtype, ctx, residual=None) -> float32
+    [rows, width]: the mixed rows, plus `residual` (which it may overwrite) when given."""
+
+    def kv_need(self) -> Optional[KVNeed]:
+        return None
+
+    def state_need(self) -> Optional[StateNeed]:
+        return None
+
+    def forward(self, h, ctx: StepContext, residual=None):
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    """forward(h [rows, width], ctx, residual=None) -> float32 [rows, width]."""
+
+    def forward(self, h, ctx: StepContext, residual=None):
+        raise NotImplementedError
+
+
+class Block(Part):
+    """forward(x float32 [rows, width], ctx) -> float32 [rows, width] (may be x itself)."""
+
+    def forward(self, x, ctx: StepContext):
+        raise NotImplementedError
+
+    def kv_need(self):
+        return None
+
+    def state_need(self):
+        return None
+
+
+NORMS: dict[str, type] = {}
+POSITION_ENCODINGS: dict[str, type] = {}
+MIXERS: dict[str, type] = {}
+FEED_FORWARDS: dict[str, type] = {}
+BLOCKS: dict[str, type] = {}
+
+
+def _register(table, what):
+    def register(kind: str, cls=None):
+        def put(c):
+            table[kind] = c
+            return c
+        return put(cls) if cls is not None else put
+    register.__doc__ = f"Registers a {what} class under a `kind` name (usable as a decorator)."
+    return register
+
+
+register_norm = _register(NORMS, "norm")
+register_position_encoding = _register(POSITION_ENCODINGS, "position encoding")
+register_mixer = _register(MIXERS, "mixer")
+register_feed_forward = _register(FEED_FORWARDS, "feed-forward")
+register_block = _register(BLOCKS, "block arrangement")
+
+
+def make(table: dict, what: str, spec, dtype, device):
+    from ..config.specs import ConfigError
+    if spec.kind not in table:
+        raise ConfigError(f"unknown {what} kind {spec.kind!r} (registered: {', '.join(sorted(table))})")
+    return table[spec.kind](spec, dtype, device)
