@@ -151,6 +151,24 @@ class Cache:
                 for i in range(min(dead_pages, len(pages))):
                     pages[i] = None
 
+    def truncate(self, slot: int, new_len: int) -> bool:
+        """Cuts a sequence back to its first `new_len` tokens (prefix reuse).  Returns False,
+        changing nothing, when a windowed group has already given back pages that the shorter
+        sequence would read again."""
+        rec = self._record(slot)
+        if not 0 <= new_len <= rec.length:
+            raise CacheError(f"slot {slot}: cannot truncate from {rec.length} to {new_len}")
+        keep = (new_len + self.page_size - 1) // self.page_size
+        for g, pages in zip(self.groups, rec.pages):
+            first_seen = max(0, new_len - g.need.window + 1) // self.page_size if g.need.window else 0
+            if any(p is None for p in pages[first_seen:keep]):
+                return False
+        for g, pages in zip(self.groups, rec.pages):
+            g.pool.give_back([p for p in pages[keep:] if p is not None])
+            del pages[keep:]
+        rec.length = new_len
+        return True
+
     def close(self, slot: int) -> None:
         """Ends a sequence: its pages and its slot go back to the pools."""
         rec = self._record(slot)

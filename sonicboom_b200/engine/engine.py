@@ -29,6 +29,17 @@ class Engine:
     def length(self, slot: int) -> int:
         return self.cache.length(slot)
 
+    @property
+    def page_size(self) -> int:
+        return self.cache.page_size
+
+    def free_pages(self) -> int:
+        """Pages every group can still hand out."""
+        return min((g.pool.free_count for g in self.cache.groups), default=0)
+
+    def free_slots(self) -> int:
+        return self.cache.slots.free_count
+
     def step(self, entries) -> torch.Tensor:
         """entries: StepEntry items or (slot, tokens, want) tuples."""
         entries = [e if isinstance(e, StepEntry) else StepEntry(e[0], list(e[1]), list(e[2]))

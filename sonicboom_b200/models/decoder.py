@@ -26,6 +26,14 @@ class DecoderModel:
         self.blocks = [make(BLOCKS, "block arrangement", l, dtype, device)
                        for l in spec.layers]
         self.final_norm = make(NORMS, "norm", spec.final_norm, dtype, device)
+        for i, e in enumerate(spec.schedule):
+            if e.cache_from is not None:
+                mine = self.blocks[e.layer].kv_need()
+                theirs = self.blocks[spec.schedule[e.cache_from].layer].kv_need()
+                if mine != theirs:
+                    from ..config.specs import ConfigError
+                    raise ConfigError(f"schedule[{i}] reads the cache of entry {e.cache_from}, "
+                                      f"whose keys and values ({theirs}) are not what it needs ({mine})")
         self.embedding = self.head = None
 
     # ------------------------------------------------------------------ weights

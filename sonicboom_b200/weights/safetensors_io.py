@@ -13,6 +13,7 @@ from __future__ import annotations
 import json
 import mmap
 import struct
+import warnings
 from pathlib import Path
 
 import torch
@@ -96,7 +97,9 @@ class SafetensorsFile:
         if e == b:
             return torch.empty(shape, dtype=dtype)
         view = memoryview(self._map)[self._data_start + b:self._data_start + e]
-        return torch.frombuffer(view, dtype=dtype).reshape(shape)
+        with warnings.catch_warnings():      # the mapping is read-only; tensors of it are only read
+            warnings.simplefilter("ignore", UserWarning)
+            return torch.frombuffer(view, dtype=dtype).reshape(shape)
 
 
 class SafetensorsDir:

@@ -1,0 +1,79 @@
+"""Shared fixtures: the tiny configurations, random model folders and the oracle's view of them.
+
+GPU tests are marked `gpu`; everything else runs on a machine without one."""
+import os
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent
+sys.path.insert(0, str(ROOT))
+sys.path.insert(0, str(Path(__file__).resolve().parent))
+
+# Three tiny configurations of the architecture that differ in every size and option:
+# layers, width, heads and groups (2:1, 6:1, 1:1), head size (16, 32, 48 with an explicit
+# head_dim that is not width/heads), intermediate size, vocabulary (none a power of two in B
+# and C), rope base, norm eps, tied or separate head, and full or windowed attention.
+TINY = {
+    "A": dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", hidden_size=64,
+              num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+              intermediate_size=160, vocab_size=256, rope_theta=10000.0, rms_norm_eps=1e-6,
+              tie_word_embeddings=True, use_sliding_window=False, max_position_embeddings=128,
+              eos_token_id=7),
+    "B": dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", hidden_size=192,
+              num_hidden_layers=3, num_attention_heads=6, num_key_value_heads=1,
+              intermediate_size=512, vocab_size=1000, rope_theta=1000000.0, rms_norm_eps=1e-5,
+              tie_word_embeddings=False, use_sliding_window=False, max_position_embeddings=256,
+              eos_token_id=[998, 999]),
+    "C": dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", hidden_size=200,
+              num_hidden_layers=4, num_attention_heads=5, num_key_value_heads=5, head_dim=48,
+              intermediate_size=136, vocab_size=1003, rope_theta=50000.0, rms_norm_eps=3e-5,
+              tie_word_embeddings=False, use_sliding_window=True, sliding_window=40,
+              max_window_layers=2, max_position_embeddings=512),
+}
+INIT = {"A": dict(std=0.02, bias_std=0.02, norm_std=0.05),
+        "B": dict(std=0.03, bias_std=0.1, norm_std=0.1),
+        "C": dict(std=0.05, bias_std=0.1, norm_std=0.1)}
+
+FP32_TOL = 1e-5      # largest |difference| / largest |reference logit|, float32 path vs oracle
+BF16_TOL = 2e-2      # same measure, bfloat16 path vs oracle
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run on a B200)")
+
+
+def pytest_collection_modifyitems(config, items):
+    if torch.cuda.is_available():
+        return
+    skip = pytest.mark.skip(reason="no CUDA device")
+    for item in items:
+        if "gpu" in item.keywords:
+            item.add_marker(skip)
+
+
+@pytest.fixture(scope="session")
+def model_dirs(tmp_path_factory):
+    """name -> folder with config.json + model.safetensors, made in a temporary place."""
+    from sonicboom_b200 import write_random_model
+    out = {}
+    for name, cfg in TINY.items():
+        d = tmp_path_factory.mktemp(f"tiny{name}")
+        write_random_model(d, cfg, seed=11 + ord(name), **INIT[name])
+        out[name] = d
+    return out
+
+
+@pytest.fixture(scope="session")
+def oracles(model_dirs):
+    """name -> (config dict, float32 tensors) as the plain implementation reads them."""
+    import plain_model
+    return {name: plain_model.read_model_dir(d) for name, d in model_dirs.items()}
+
+
+def prompts_for(name: str, lengths, seed=0):
+    g = torch.Generator().manual_seed(seed + ord(name))
+    vocab = TINY[name]["vocab_size"]
+    return [torch.randint(0, vocab, (n,), generator=g).tolist() for n in lengths]

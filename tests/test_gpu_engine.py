@@ -1,0 +1,108 @@
+"""The engine against the plain implementation, in float32 and in bfloat16: each request alone
+and whole; with its last 32 tokens one by one; in batches of unequal lengths whose shorter
+requests end earlier, one batch after another so that slots are used again; long decoding; the
+first tokens of a sequence."""
+import pytest
+import torch
+
+import plain_model as pm
+from conftest import BF16_TOL, FP32_TOL, TINY, prompts_for
+from gpu_util import batch_unequal, engine_for, oracle_logits, tail_one_by_one, whole
+
+pytestmark = pytest.mark.gpu
+TOL = {"float32": FP32_TOL, "bfloat16": BF16_TOL}
+LENGTHS = {"A": [5, 11, 17, 90], "B": [1, 7, 33, 64, 100], "C": [3, 40, 41, 65, 130, 200]}
+CASES = [(n, d) for n in TINY for d in ("float32", "bfloat16")]
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_each_request_alone_and_whole(model_dirs, oracles, name, dtype):
+    eng = engine_for(model_dirs, name, dtype)
+    for p in prompts_for(name, LENGTHS[name]):
+        err = pm.rel_err(whole(eng, p), oracle_logits(oracles, name, p))
+        assert err < TOL[dtype], f"{name} {dtype} length {len(p)}: {err}"
+    eng.cache.check()
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_last_32_tokens_one_by_one(model_dirs, oracles, name, dtype):
+    eng = engine_for(model_dirs, name, dtype)
+    for p in prompts_for(name, [33, LENGTHS[name][-1]], seed=1):
+        ref = oracle_logits(oracles, name, p)
+        got = tail_one_by_one(eng, p, 32)
+        err = pm.rel_err(got, ref)
+        assert err < TOL[dtype], f"{name} {dtype} length {len(p)}: {err}"
+        if dtype == "float32":     # cutting changes nothing beyond rounding
+            assert pm.rel_err(got, whole(eng, p)) < FP32_TOL
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_unequal_batches_one_after_another(model_dirs, oracles, name, dtype):
+    lengths = LENGTHS[name]
+    cache_tokens = sum((n + 63) // 64 * 64 for n in lengths)
+    eng = engine_for(model_dirs, name, dtype, max_tokens=cache_tokens)   # exactly what one batch holds
+    seen_slots = []
+    for round_ in range(3):                                              # slots and pages are used again
+        reqs = prompts_for(name, lengths[::-1] if round_ % 2 else lengths, seed=10 + round_)
+        prompt_lens = [max(1, len(r) - (3 + 5 * i)) for i, r in enumerate(reqs)]
+        before = set(eng.cache.records)
+        got = batch_unequal(eng, reqs, prompt_lens)
+        assert not eng.cache.records and before == set()
+        for r, g in zip(reqs, got):
+            err = pm.rel_err(g, oracle_logits(oracles, name, r))
+            assert err < TOL[dtype], f"{name} {dtype} round {round_} length {len(r)}: {err}"
+        eng.cache.check()
+    assert all(g.pool.free_count == g.pool.n for g in eng.cache.groups)
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_long_decoding(model_dirs, oracles, name, dtype):
+    n = TINY[name]["max_position_embeddings"] if name != "C" else 300
+    eng = engine_for(model_dirs, name, dtype)
+    (p,) = prompts_for(name, [n], seed=2)
+    got = tail_one_by_one(eng, p, n - 4)           # 4 prompt tokens, everything else decoded
+    err = pm.rel_err(got, oracle_logits(oracles, name, p))
+    assert err < TOL[dtype], f"{name} {dtype}: {err}"
+    # the worst single position, to show where an error would sit (page edges: 64, 128, ...)
+    ref = oracle_logits(oracles, name, p)
+    per_pos = (got - ref).abs().amax(dim=1) / ref.abs().max()
+    assert float(per_pos.max()) < TOL[dtype], f"worst position {int(per_pos.argmax())}"
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_first_tokens_of_a_sequence(model_dirs, oracles, name, dtype):
+    eng = engine_for(model_dirs, name, dtype)
+    reqs = prompts_for(name, [6, 6, 6], seed=3)
+    got = batch_unequal(eng, reqs, [1, 2, 1])       # decoding starts right after the first token
+    for r, g in zip(reqs, got):
+        ref = oracle_logits(oracles, name, r)
+        assert pm.rel_err(g, ref) < TOL[dtype]
+        assert pm.rel_err(g[:2], ref[:2]) < TOL[dtype] * float(ref.abs().max() / ref[:2].abs().max())
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_batch_position_and_neighbours_do_not_matter(model_dirs, dtype):
+    """A request's logits are the same alone, first, last or in the middle of a batch."""
+    eng = engine_for(model_dirs, "B", dtype)
+    reqs = prompts_for("B", [70, 9, 33], seed=4)
+    alone = [whole(eng, r) for r in reqs]
+    for order in ([0, 1, 2], [2, 0, 1], [1, 2, 0]):
+        got = batch_unequal(eng, [reqs[i] for i in order], [len(reqs[i]) for i in order])
+        for i, g in zip(order, got):
+            assert pm.rel_err(g, alone[i]) < (1e-6 if dtype == "float32" else BF16_TOL), (order, i)
+
+
+def test_refusals_reach_the_caller(model_dirs):
+    from sonicboom_b200 import StepError
+    from sonicboom_b200.cache import CacheFull
+    eng = engine_for(model_dirs, "A", "float32", max_tokens=128)
+    s = eng.open()
+    with pytest.raises(StepError, match="outside the vocabulary"):
+        eng.step([(s, [256], [0])])
+    with pytest.raises(StepError, match="max_position_embeddings"):
+        eng.step([(s, [1] * 129, [])])
+    t = eng.open()
+    eng.step([(s, [1] * 100, [])])
+    with pytest.raises(CacheFull):
+        eng.step([(t, [1] * 10, [])])
+    assert eng.step([(s, [2], [])]) is None

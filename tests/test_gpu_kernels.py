@@ -1,0 +1,356 @@
+"""Each kernel alone against a plain float32 reference, at sizes other than the models'.
+
+Where random inputs would hide a fault, the inputs are made so that it shows: one far key
+among hundreds carries the whole softmax, keys sit exactly on a window's two edges, and every
+sequence of a batch finds a value that names its own slot and position."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_model as pm
+import plain_sampling as ps
+from sonicboom_b200 import ops
+from sonicboom_b200.cache import Cache, KVNeed
+from sonicboom_b200.engine.step import StepEntry, StepPlan
+from sonicboom_b200.parts.feedforward import interleave_gate_up
+from sonicboom_b200.sampling import Sampler, Sampling
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+
+
+def rnd(*shape, dtype=torch.float32, scale=1.0, seed=0):
+    g = torch.Generator().manual_seed(seed + sum(shape))
+    return (torch.randn(*shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+def close(got, ref, tol):
+    err = pm.rel_err(got.float().cpu(), ref.float().cpu())
+    assert err < tol, err
+
+
+# --------------------------------------------------------------------------- small kernels
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_embed(dtype):
+    table = rnd(517, 72, dtype=DT[dtype])
+    tokens = torch.tensor([0, 516, 3, 3, 100], dtype=torch.int32, device=DEV)
+    out = torch.empty(5, 72, device=DEV)
+    ops.embed(tokens, table, out)
+    assert torch.equal(out, table.float()[tokens.long()])
+
+
+@pytest.mark.parametrize("width", [8, 72, 1000, 3584])
+@pytest.mark.parametrize("wdtype,odtype", [("float32", "float32"), ("bfloat16", "bfloat16"),
+                                           ("float32", "bfloat16")])
+def test_rmsnorm(width, wdtype, odtype):
+    x = rnd(7, width, scale=3.0)
+    w = rnd(width, dtype=DT[wdtype]) + 1
+    out = torch.empty(7, width, dtype=DT[odtype], device=DEV)
+    ops.rmsnorm(x, w, 1e-5, out)
+    ref = pm.rms_norm(x.cpu(), w.float().cpu(), 1e-5)
+    close(out, ref, 1e-6 if odtype == "float32" else 5e-3)
+    rows = torch.tensor([6, 0, 6], dtype=torch.int32, device=DEV)
+    g = torch.empty(3, width, dtype=DT[odtype], device=DEV)
+    ops.rmsnorm(x, w, 1e-5, g, rows)
+    assert torch.equal(g, out[rows.long()])
+    # a row's result does not depend on the other rows of the launch
+    one = torch.empty(1, width, dtype=DT[odtype], device=DEV)
+    ops.rmsnorm(x[3:4].contiguous(), w, 1e-5, one)
+    assert torch.equal(one[0], out[3])
+
+
+def test_cast_round_trip():
+    x = rnd(1000, 3)
+    b = ops.cast(x, torch.bfloat16)
+    assert torch.equal(b, x.to(torch.bfloat16)) and torch.equal(ops.cast(b, torch.float32), b.float())
+
+
+# --------------------------------------------------------------------------------- products
+
+def linear_ref(a, w, epilogue, bias, residual):
+    y = a.double().cpu() @ w.double().cpu().t()
+    if epilogue == ops.EPI_BIAS:
+        y = y + bias.double().cpu()
+    elif epilogue == ops.EPI_RESIDUAL:
+        y = y + residual.double().cpu()
+    elif epilogue == ops.EPI_SWIGLU:
+        n = y.shape[1] // 2
+        blocks = y.view(y.shape[0], n // 8, 2, 8)
+        g, u = blocks[:, :, 0, :].reshape(-1, n), blocks[:, :, 1, :].reshape(-1, n)
+        y = g / (1 + torch.exp(-g)) * u
+    return y.float()
+
+
+SHAPES = [(1, 24, 40), (3, 152, 72), (17, 1000, 200), (64, 96, 1024), (65, 264, 136),
+          (200, 520, 328), (333, 128, 2048)]
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES)
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("kernel", ["plain", "auto"])
+def test_linear_epilogues(M, N, K, dtype, kernel):
+    if dtype == "float32" and kernel == "auto":
+        pytest.skip("float32 has the plain kernel only")
+    dt = DT[dtype]
+    a, w = rnd(M, K, dtype=dt), rnd(N, K, dtype=dt, scale=K ** -0.5, seed=1)
+    bias, res = rnd(N, dtype=dt, seed=2), rnd(M, N, seed=3)
+    tol = 2e-6 if dtype == "float32" else 1e-5      # float32 accumulation of exact bf16 products
+    for epi, odt in [(ops.EPI_NONE, torch.float32), (ops.EPI_BIAS, torch.float32),
+                     (ops.EPI_RESIDUAL, torch.float32), (ops.EPI_SWIGLU, dt),
+                     (ops.EPI_NONE, dt)]:
+        if epi == ops.EPI_SWIGLU and N % 16:
+            continue
+        out = torch.empty(M, N // 2 if epi == ops.EPI_SWIGLU else N, dtype=odt, device=DEV)
+        r = res.clone()
+        ops.linear(a, w, out, epi, bias=bias if epi == ops.EPI_BIAS else None,
+                   residual=r if epi == ops.EPI_RESIDUAL else None, kernel=kernel)
+        close(out, linear_ref(a, w, epi, bias, res), tol if odt == torch.float32 else 5e-3)
+        if epi == ops.EPI_RESIDUAL:                 # in place on the residual stream
+            ops.linear(a, w, r, epi, residual=r, kernel=kernel)
+            assert torch.equal(r, out)
+
+
+@pytest.mark.parametrize("kernel", ["plain", "auto"])
+def test_linear_rows_do_not_depend_on_the_batch(kernel):
+    a, w = rnd(40, 256, dtype=torch.bfloat16), rnd(88, 256, dtype=torch.bfloat16, seed=1)
+    full = torch.empty(40, 88, device=DEV)
+    ops.linear(a, w, full, kernel=kernel)
+    for rows in (slice(0, 1), slice(5, 12), slice(39, 40)):
+        part = torch.empty(rows.stop - rows.start, 88, device=DEV)
+        ops.linear(a[rows].contiguous(), w, part, kernel=kernel)
+        assert pm.rel_err(part.cpu(), full[rows].cpu()) < 1e-6
+
+
+def test_fused_gate_up_layout():
+    gate, up = rnd(32, 8), rnd(32, 8, seed=1)
+    f = interleave_gate_up(gate, up)
+    assert torch.equal(f[0:8], gate[0:8]) and torch.equal(f[8:16], up[0:8])
+    assert torch.equal(f[48:56], gate[24:32]) and torch.equal(f[56:64], up[24:32])
+
+
+def test_linear_refuses_what_it_cannot_do():
+    a, w = rnd(2, 8), rnd(24, 8)
+    with pytest.raises(ops.KernelError, match="multiple of 8"):
+        ops.linear(a, w, torch.empty(2, 12, device=DEV), ops.EPI_SWIGLU)
+    with pytest.raises(ops.KernelError, match="CUDA tensors only"):
+        ops.linear(a.cpu(), w, torch.empty(2, 24, device=DEV))
+    with pytest.raises(ops.KernelError, match="float32"):
+        ops.linear(a, w, torch.empty(2, 24, dtype=torch.bfloat16, device=DEV), ops.EPI_RESIDUAL,
+                   residual=torch.zeros(2, 24, device=DEV))
+
+
+# ----------------------------------------------------------------- rotation + cache + attention
+
+def make_cache(hkv, hd, window, dtype, max_tokens=2048):
+    return Cache([KVNeed(hkv, hd, window)], [None], max_tokens, dtype, DEV)
+
+
+def run_attention(cache, hq, hkv, hd, window, dtype, seqs, rot=None, theta=10000.0, scale=None,
+                  kernel="auto"):
+    """seqs: list of (slot, qkv float32 [n, (hq+2hkv)*hd]).  Writes k, v and returns attention
+    output [rows, hq*hd] plus the rotated q."""
+    rot = hd if rot is None else rot
+    for s, x in seqs:
+        cache.reserve(s, cache.length(s) + x.shape[0])
+    plan = StepPlan(cache, [StepEntry(s, [0] * x.shape[0], []) for s, x in seqs], DEV)
+    qkv = torch.cat([x for _, x in seqs]).to(DEV)
+    i = np.arange(max(rot // 2, 1), dtype=np.float32)
+    inv = torch.from_numpy(np.exp(-2.0 * i / np.float32(max(rot, 1)) * np.log(np.float32(theta)))
+                           .astype(np.float32)).to(DEV)
+    q = torch.empty(qkv.shape[0], hq, hd, dtype=dtype, device=DEV)
+    g = plan.groups[0]
+    storage = cache.groups[0].entry_storage(0)
+    ops.rope_store(qkv, hq, hkv, hd, rot, inv, plan.row_seq, plan.row_pos, g.page_off, g.page_ids,
+                   g.page_size, storage, q)
+    out = torch.empty(qkv.shape[0], hq * hd, dtype=dtype, device=DEV)
+    ops.attention(q, out, plan, 0, storage, hq, hkv, hd, window,
+                  scale if scale is not None else hd ** -0.5, kernel=kernel)
+    for s, x in seqs:
+        cache.advance(s, cache.length(s) + x.shape[0])
+    return out.float().cpu(), q.float().cpu()
+
+
+def attention_ref(qkv, pos0, hq, hkv, hd, window, history=None, theta=10000.0, scale=None):
+    """Plain implementation on one sequence; `history` is earlier rows' qkv."""
+    allx = qkv if history is None else torch.cat([history, qkv])
+    n = allx.shape[0]
+    pos = torch.arange(n)
+    q = pm.rope_neox(allx[:, :hq * hd].reshape(n, hq, hd), pos, theta)
+    k = pm.rope_neox(allx[:, hq * hd:(hq + hkv) * hd].reshape(n, hkv, hd), pos, theta)
+    v = allx[:, (hq + hkv) * hd:].reshape(n, hkv, hd)
+    out = pm.attention(q, k, v, pos, pos, scale if scale is not None else hd ** -0.5, window)
+    return out[n - qkv.shape[0]:].reshape(qkv.shape[0], hq * hd)
+
+
+@pytest.mark.parametrize("hq,hkv,hd", [(4, 2, 16), (6, 1, 32), (5, 5, 48), (14, 2, 64), (28, 4, 128),
+                                       (3, 1, 80), (8, 8, 256)])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("kernel", ["plain", "auto"])
+def test_rotation_cache_and_attention(hq, hkv, hd, dtype, kernel):
+    if dtype == "float32" and kernel == "auto":
+        pytest.skip("float32 has the plain kernel only")
+    tol = 2e-6 if dtype == "float32" else 1.5e-2
+    for window in (0, 37):
+        cache = make_cache(hkv, hd, window, DT[dtype])
+        lens = [1, 70, 150]
+        xs = [torch.randn(n, (hq + 2 * hkv) * hd, generator=torch.Generator().manual_seed(n)) for n in lens]
+        slots = [cache.open() for _ in lens]
+        out, _ = run_attention(cache, hq, hkv, hd, window, DT[dtype], list(zip(slots, xs)), kernel=kernel)
+        at = 0
+        for x in xs:
+            close(out[at:at + x.shape[0]], attention_ref(x, 0, hq, hkv, hd, window), tol)
+            at += x.shape[0]
+        # then decode: one more row for each sequence, then 3 more for one of them
+        for n_new in (1, 3):
+            news = [torch.randn(n_new, xs[0].shape[1], generator=torch.Generator().manual_seed(7 + i))
+                    for i in range(len(xs))]
+            out, _ = run_attention(cache, hq, hkv, hd, window, DT[dtype], list(zip(slots, news)),
+                                   kernel=kernel)
+            for i, (x, new) in enumerate(zip(xs, news)):
+                close(out[i * n_new:(i + 1) * n_new],
+                      attention_ref(new, x.shape[0], hq, hkv, hd, window, history=x), tol)
+            xs = [torch.cat([x, new]) for x, new in zip(xs, news)]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("kernel", ["plain", "auto"])
+def test_partial_rotation_and_no_rotation(dtype, kernel):
+    if dtype == "float32" and kernel == "auto":
+        pytest.skip("float32 has the plain kernel only")
+    hq, hkv, hd = 4, 2, 32
+    x = torch.randn(9, (hq + 2 * hkv) * hd, generator=torch.Generator().manual_seed(1))
+    for rot in (0, 16):
+        cache = make_cache(hkv, hd, 0, DT[dtype])
+        _, q = run_attention(cache, hq, hkv, hd, 0, DT[dtype], [(cache.open(), x)], rot=rot, kernel=kernel)
+        ref = x[:, :hq * hd].reshape(9, hq, hd).clone()
+        if rot:
+            ref[..., :rot] = pm.rope_neox(ref[..., :rot].contiguous(), torch.arange(9), 10000.0)
+        close(q, ref, 1e-6 if dtype == "float32" else 5e-3)
+
+
+def standout(n, hq, hkv, hd, key_pos, big=60.0):
+    """qkv rows (no rotation is applied by the caller) where every query matches only the key
+    at `key_pos`, strongly, and v rows spell (position + 1) in every component."""
+    qkv = torch.zeros(n, (hq + 2 * hkv) * hd)
+    qkv[:, :hq * hd] = 0.01 * torch.randn(n, hq * hd, generator=torch.Generator().manual_seed(5))
+    qkv[:, 0:hq * hd:hd] = 1.0                            # component 0 of every query head
+    k = qkv[:, hq * hd:(hq + hkv) * hd].view(n, hkv, hd)
+    k[key_pos, :, 0] = big / (hd ** -0.5)
+    v = qkv[:, (hq + hkv) * hd:].view(n, hkv, hd)
+    v += (torch.arange(n, dtype=torch.float32) + 1)[:, None, None]
+    return qkv
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("kernel", ["plain", "auto"])
+def test_a_far_key_among_hundreds_is_found(dtype, kernel):
+    if dtype == "float32" and kernel == "auto":
+        pytest.skip("float32 has the plain kernel only")
+    hq, hkv, hd, n = 6, 2, 32, 700
+    for key_pos in (3, 64, 255, 256, 511, 640):
+        cache = make_cache(hkv, hd, 0, DT[dtype])
+        s = cache.open()
+        x = standout(n, hq, hkv, hd, key_pos)
+        out, _ = run_attention(cache, hq, hkv, hd, 0, DT[dtype], [(s, x[:n - 1])], rot=0, kernel=kernel)
+        last = out[-1]                                    # prefill row n-2 sees the key
+        assert abs(float(last.mean()) - (key_pos + 1)) < 0.02 * (key_pos + 1), (key_pos, float(last.mean()))
+        out, _ = run_attention(cache, hq, hkv, hd, 0, DT[dtype], [(s, x[n - 1:])], rot=0, kernel=kernel)
+        assert abs(float(out.mean()) - (key_pos + 1)) < 0.02 * (key_pos + 1), (key_pos, float(out.mean()))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("kernel", ["plain", "auto"])
+def test_window_edges(dtype, kernel):
+    """Query i sees key j iff i - j < window: the key at i - window + 1 counts, i - window not."""
+    if dtype == "float32" and kernel == "auto":
+        pytest.skip("float32 has the plain kernel only")
+    hq, hkv, hd, window = 4, 2, 16, 70
+    for n in (71, 135, 200):                              # the last row is the query
+        i = n - 1
+        for key_pos, seen in ((i - window + 1, True), (i - window, False)):
+            for decode in (False, True):
+                cache = make_cache(hkv, hd, window, DT[dtype])
+                s = cache.open()
+                x = standout(n, hq, hkv, hd, key_pos)
+                if decode:
+                    run_attention(cache, hq, hkv, hd, window, DT[dtype], [(s, x[:i])], rot=0, kernel=kernel)
+                    out, _ = run_attention(cache, hq, hkv, hd, window, DT[dtype], [(s, x[i:])], rot=0,
+                                           kernel=kernel)
+                else:
+                    out, _ = run_attention(cache, hq, hkv, hd, window, DT[dtype], [(s, x)], rot=0,
+                                           kernel=kernel)
+                got = float(out[-1].mean())
+                if seen:
+                    assert abs(got - (key_pos + 1)) < 0.02 * (key_pos + 1), (n, key_pos, decode, got)
+                else:                                     # an average over the window's own keys
+                    assert i - window + 2 <= got <= i + 1, (n, key_pos, decode, got)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("kernel", ["plain", "auto"])
+def test_every_sequence_reads_its_own_pages(dtype, kernel):
+    if dtype == "float32" and kernel == "auto":
+        pytest.skip("float32 has the plain kernel only")
+    hq, hkv, hd = 4, 1, 16
+    cache = make_cache(hkv, hd, 0, DT[dtype], max_tokens=64 * 40)
+    # interleave the sequences' growth so that their pages are interleaved in the pool
+    slots = [cache.open() for _ in range(4)]
+    lens = [130, 5, 260, 64]
+    keys = [100, 2, 7, 63]
+    xs = [standout(n + 1, hq, hkv, hd, k) for n, k in zip(lens, keys)]
+    for i, x in enumerate(xs):                            # values name the sequence too
+        x[:, (hq + hkv) * hd:] += 1000.0 * i
+    fed = [0] * 4
+    while any(f < n for f, n in zip(fed, lens)):
+        step = [(s, x[f:min(f + 50, n)]) for s, x, f, n in zip(slots, xs, fed, lens) if f < n]
+        run_attention(cache, hq, hkv, hd, 0, DT[dtype], step, rot=0, kernel=kernel)
+        fed = [min(f + 50, n) for f, n in zip(fed, lens)]
+    out, _ = run_attention(cache, hq, hkv, hd, 0, DT[dtype],
+                           [(s, x[n:]) for s, x, n in zip(slots, xs, lens)], rot=0, kernel=kernel)
+    for i, k in enumerate(keys):
+        want = 1000.0 * i + k + 1
+        assert abs(float(out[i].mean()) - want) < 0.01 * want + 0.5, (i, float(out[i].mean()), want)
+    pages = [cache.page_list(s, 0) for s in slots]
+    assert pages[0][1] != pages[0][0] + 1                 # the pool really was interleaved
+
+
+# --------------------------------------------------------------------------------- sampling
+
+def test_sampler_matches_the_plain_sampler():
+    sampler = Sampler(DEV)
+    g = torch.Generator().manual_seed(0)
+    for vocab in (50, 256, 1003, 152064):
+        logits = (torch.randn(6, vocab, generator=g) * 3).to(DEV)
+        logits[1, :] = 0.25                               # all tied: lowest ids win
+        logits[2, vocab // 2] = 40.0
+        hist = [list(range(0, 40)), [1, 1, 2], [vocab // 2] * 5, [], [3, 4], [vocab - 1]]
+        cases = [Sampling(), Sampling(temperature=0.8, seed=5), Sampling(temperature=1.5, top_k=7, seed=1),
+                 Sampling(temperature=1.0, top_p=0.7, seed=2 ** 50), Sampling(temperature=0.6, min_p=0.1, seed=3),
+                 Sampling(temperature=0.9, seed=4, repeat_penalty=1.3, presence_penalty=0.5,
+                          frequency_penalty=0.25, repeat_last_n=16),
+                 Sampling(repeat_penalty=5.0, presence_penalty=100.0)]
+        for s in cases:
+            s = s.checked()
+            before = logits.clone()
+            for position in (0, 17, 2 ** 33 + 1):
+                got = sampler.sample(logits, [s] * 6, [position + r for r in range(6)], hist)
+                want = [ps.sample_token(logits[r].cpu().numpy(),
+                                        ps.Params(s.temperature, s.top_k, s.top_p, s.min_p, s.seed,
+                                                  s.repeat_penalty, s.repeat_last_n, s.presence_penalty,
+                                                  s.frequency_penalty), position + r, hist[r])
+                        for r in range(6)]
+                assert got == want, (vocab, s, position)
+            assert torch.equal(logits, before)            # penalties were undone
+
+
+def test_sampled_tokens_do_not_depend_on_the_row():
+    sampler = Sampler(DEV)
+    logits = (torch.randn(4, 500, generator=torch.Generator().manual_seed(2)) * 2).to(DEV)
+    s = Sampling(temperature=1.0, seed=9).checked()
+    a = sampler.sample(logits, [s] * 4, [10, 11, 12, 13], [[]] * 4)
+    b = sampler.sample(logits.flip(0).contiguous(), [s] * 4, [13, 12, 11, 10], [[]] * 4)
+    assert a == b[::-1]
