@@ -98,7 +98,7 @@ def test_linear_epilogues(M, N, K, dtype, kernel):
     dt = DT[dtype]
     a, w = rnd(M, K, dtype=dt), rnd(N, K, dtype=dt, scale=K ** -0.5, seed=1)
     bias, res = rnd(N, dtype=dt, seed=2), rnd(M, N, seed=3)
-    tol = 2e-6 if dtype == "float32" else 1e-5      # float32 accumulation of exact bf16 products
+    tol = 1e-5      # float32 accumulation over up to 2048 terms (typical error sqrt(K) * 6e-8)
     for epi, odt in [(ops.EPI_NONE, torch.float32), (ops.EPI_BIAS, torch.float32),
                      (ops.EPI_RESIDUAL, torch.float32), (ops.EPI_SWIGLU, dt),
                      (ops.EPI_NONE, dt)]:
@@ -193,7 +193,7 @@ def attention_ref(qkv, pos0, hq, hkv, hd, window, history=None, theta=10000.0, s
 def test_rotation_cache_and_attention(hq, hkv, hd, dtype, kernel):
     if dtype == "float32" and kernel == "auto":
         pytest.skip("float32 has the plain kernel only")
-    tol = 2e-6 if dtype == "float32" else 1.5e-2
+    tol = 1e-5 if dtype == "float32" else 1.5e-2
     for window in (0, 37):
         cache = make_cache(hkv, hd, window, DT[dtype])
         lens = [1, 70, 150]
