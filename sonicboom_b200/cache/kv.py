@@ -48,7 +48,9 @@ class CacheGroup:
                  device):
         self.need, self.entries, self.page_size = need, list(entries), page_size
         self.pool = FreeList(n_pages, "page")
-        self.storage = torch.empty((len(entries), n_pages, 2, need.n_kv_heads, page_size,
+        # zeroed once: a page's unused tail is multiplied by zero probabilities, so it must
+        # never hold NaN or infinity bit patterns; what sequences write later is finite
+        self.storage = torch.zeros((len(entries), n_pages, 2, need.n_kv_heads, page_size,
                                     need.head_dim), dtype=dtype, device=device)
         self._index = {e: i for i, e in enumerate(entries)}
 

@@ -1,0 +1,484 @@
+// Causal grouped-query attention over the paged cache on tensor cores (mma.sync m16n8k16,
+// bfloat16 operands, float32 scores, softmax statistics and output accumulator).
+//
+// This file is compiled once per head size (-DSB_HD=<multiple of 16, at most 256>) into a
+// library of its own, so a model pays only for the head size it has.
+//
+// Rows.  For one sequence and one key/value head, the query rows are the pairs
+// (new token t, query head g of the group): row r = t * G + g.  All G query heads that share a
+// key/value head therefore share every key and value tile that is loaded, in prefill and in
+// decode alike (the reference's tensor-core kernels pack the group the same way,
+// core/src/nn/boom_fdec_device.cuh:17-30, core/src/nn/boom_fattn.cu:37-84).
+//
+//  * prefill kernel: 64 rows per block (4 warps x 16), key tiles of one cache page (64 keys)
+//    taken in ascending order with a double-buffered cp.async pipeline, online softmax.
+//  * decode kernel (at most 16 rows per sequence and head): the keys are cut into splits of 256
+//    at absolute positions; a block takes one split, each of its 4 warps one page of it; the
+//    warps' partial (m, l, o) are merged in warp order, and when a sequence has more than one
+//    split the blocks' partials go to scratch memory and a second kernel merges them in
+//    ascending order (core/src/model/emit.cpp:538-560 "chunk_index_asc",
+//    core/src/nn/cuda_elementwise.cu:852-1017).  Tile and split boundaries depend only on
+//    key positions, so a result does not depend on the batch or on where the pages lie.
+//
+// Mask: key j is visible to the query at position i when j <= i and (window == 0 or
+// i - j < window) (core/src/nn/attention.cpp:66-70).  The scale multiplies the finished dot
+// product in float32.  Probabilities are rounded to bfloat16 only as the P.V operand.
+#include <math.h>
+
+#include "common.cuh"
+
+#ifndef SB_HD
+#define SB_HD 128
+#endif
+
+namespace {
+
+typedef __nv_bfloat16 bf16;
+constexpr int HD = SB_HD;
+constexpr int KT = 64;                 // keys per tile = cache page size
+constexpr int LDS = HD + 8;            // shared-memory row stride: an odd number of 16-byte chunks
+constexpr int BM = 64;                 // prefill rows per block
+constexpr int SPLIT_PAGES = 4;         // decode: pages per split (256 keys)
+constexpr int DEC_ROWS = 16;
+constexpr float LOG2E = 1.4426950408889634f;
+
+static_assert(HD % 16 == 0 && HD >= 16 && HD <= 256, "head size in steps of 16, at most 256");
+
+struct AttnParams {
+  const bf16* q;               // [rows, n_q_heads, HD]
+  bf16* out;                   // [rows, n_q_heads * HD]
+  const int32_t* seq_row0;     // [n_seqs + 1]
+  const int32_t* seq_pos0;     // [n_seqs] position of a sequence's first new row
+  const int32_t* page_off;     // [n_seqs + 1]
+  const int32_t* page_ids;
+  const bf16* cache;           // [page][k|v][kv head][KT][HD]
+  float* scratch;
+  int n_q_heads, n_kv_heads, window, n_splits;
+  float scale_log2;            // scale * log2(e)
+};
+
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0,
+                                         uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+      "{%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
+  const int bytes = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1,
+                                            uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1,
+                                                  uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Copies one cache page's K and V tiles of a key/value head into shared memory.
+__device__ __forceinline__ void load_kv_tile(uint32_t ks, uint32_t vs, const bf16* cache, int page,
+                                             int n_kv_heads, int kvh, int tid, int n_threads) {
+  const bf16* kbase = cache + (((size_t)page * 2) * n_kv_heads + kvh) * (size_t)(KT * HD);
+  const bf16* vbase = kbase + (size_t)n_kv_heads * (KT * HD);
+  for (int idx = tid; idx < KT * (HD / 8); idx += n_threads) {
+    const int row = idx / (HD / 8), ch = idx % (HD / 8);
+    const uint32_t off = (uint32_t)(row * LDS + ch * 8) * 2;
+    cp_async16(ks + off, kbase + row * HD + ch * 8, true);
+    cp_async16(vs + off, vbase + row * HD + ch * 8, true);
+  }
+}
+
+// One key tile for a warp's 16 rows: scores, mask, online softmax update, P.V.
+// `pos_a`, `pos_b`: positions of the thread's two rows (g and g + 8), -1 for padding rows.
+__device__ __forceinline__ void tile_step(const uint32_t (&qf)[HD / 16][4], uint32_t ks,
+                                          uint32_t vs, int key0, int pos_a, int pos_b, int window,
+                                          float scale_log2, float (&m)[2], float (&l)[2],
+                                          float (&o)[HD / 8][4], int lane) {
+  float s[KT / 8][4];
+#pragma unroll
+  for (int j = 0; j < KT / 8; ++j)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) s[j][i] = 0.0f;
+#pragma unroll
+  for (int kk = 0; kk < HD / 16; ++kk) {
+#pragma unroll
+    for (int j = 0; j < KT / 16; ++j) {
+      const int row = j * 16 + (lane & 7) + ((lane >> 4) << 3);
+      const int col = kk * 16 + ((lane >> 3) & 1) * 8;
+      uint32_t b0, b1, b2, b3;
+      ldmatrix_x4(ks + (uint32_t)(row * LDS + col) * 2, b0, b1, b2, b3);
+      mma_bf16(s[2 * j], qf[kk], b0, b1);
+      mma_bf16(s[2 * j + 1], qf[kk], b2, b3);
+    }
+  }
+  const int t = lane & 3;
+  float tmax[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+  for (int j = 0; j < KT / 8; ++j) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int key = key0 + j * 8 + 2 * t + (i & 1);
+      const int pos = (i < 2) ? pos_a : pos_b;
+      const bool seen = key <= pos && (window == 0 || pos - key < window);
+      const float v = seen ? s[j][i] * scale_log2 : -INFINITY;
+      s[j][i] = v;
+      tmax[i >> 1] = fmaxf(tmax[i >> 1], v);
+    }
+  }
+  float alpha[2], base[2];
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 1));
+    tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 2));
+    const float m_new = fmaxf(m[r], tmax[r]);
+    base[r] = m_new == -INFINITY ? 0.0f : m_new;          // nothing seen yet: exp2(-inf - 0) = 0
+    alpha[r] = exp2f(m[r] - base[r]);
+    m[r] = m_new;
+    l[r] *= alpha[r];
+  }
+#pragma unroll
+  for (int j = 0; j < HD / 8; ++j) {
+    o[j][0] *= alpha[0]; o[j][1] *= alpha[0];
+    o[j][2] *= alpha[1]; o[j][3] *= alpha[1];
+  }
+#pragma unroll
+  for (int j = 0; j < KT / 8; ++j) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float p = exp2f(s[j][i] - base[i >> 1]);
+      s[j][i] = p;
+      l[i >> 1] += p;
+    }
+  }
+#pragma unroll
+  for (int kk = 0; kk < KT / 16; ++kk) {
+    uint32_t a[4];
+    a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+    a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+    a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+    a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+    for (int dj = 0; dj < HD / 16; ++dj) {
+      const int row = kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+      const int col = dj * 16 + (lane >> 4) * 8;
+      uint32_t b0, b1, b2, b3;
+      ldmatrix_x4_trans(vs + (uint32_t)(row * LDS + col) * 2, b0, b1, b2, b3);
+      mma_bf16(o[2 * dj], a, b0, b1);
+      mma_bf16(o[2 * dj + 1], a, b2, b3);
+    }
+  }
+}
+
+__device__ __forceinline__ void load_q_frags(uint32_t qs, int warp_row0, int lane,
+                                             uint32_t (&qf)[HD / 16][4]) {
+#pragma unroll
+  for (int kk = 0; kk < HD / 16; ++kk) {
+    const int row = warp_row0 + (lane & 15), col = kk * 16 + (lane >> 4) * 8;
+    ldmatrix_x4(qs + (uint32_t)(row * LDS + col) * 2, qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3]);
+  }
+}
+
+// ------------------------------------------------------------------------------- prefill
+constexpr int PREFILL_SMEM = (BM + 4 * KT) * LDS * 2;
+
+__global__ void __launch_bounds__(128) attn_prefill_kernel(const AttnParams p) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  const uint32_t qs = (uint32_t)__cvta_generic_to_shared(smem);
+  const uint32_t kv0 = qs + BM * LDS * 2;                     // K0, V0, K1, V1
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int b = blockIdx.z, kvh = blockIdx.y;
+  const int G = p.n_q_heads / p.n_kv_heads;
+  const int row0 = p.seq_row0[b], n_new = p.seq_row0[b + 1] - row0, pos0 = p.seq_pos0[b];
+  const int R = n_new * G, r_base = blockIdx.x * BM;
+  if (r_base >= R) return;
+  const int32_t* pages = p.page_ids + p.page_off[b];
+
+  for (int idx = tid; idx < BM * (HD / 8); idx += 128) {
+    const int row = idx / (HD / 8), ch = idx % (HD / 8);
+    const int r = r_base + row;
+    const bool valid = r < R;
+    const int t = valid ? r / G : 0, g = valid ? r % G : 0;
+    cp_async16(qs + (uint32_t)(row * LDS + ch * 8) * 2,
+               p.q + ((size_t)(row0 + t) * p.n_q_heads + kvh * G + g) * HD + ch * 8, valid);
+  }
+  const int r_last = min(R, r_base + BM) - 1;
+  const int p_lo = pos0 + r_base / G, p_hi = pos0 + r_last / G;
+  const int tile_lo = (p.window > 0 ? max(0, p_lo - p.window + 1) : 0) / KT, tile_hi = p_hi / KT;
+  load_kv_tile(kv0, kv0 + KT * LDS * 2, p.cache, pages[tile_lo], p.n_kv_heads, kvh, tid, 128);
+  cp_async_commit();
+  cp_async_wait<0>();
+  __syncthreads();
+
+  uint32_t qf[HD / 16][4];
+  load_q_frags(qs, warp * 16, lane, qf);
+  const int ra = r_base + warp * 16 + (lane >> 2), rb = ra + 8;
+  const int pos_a = ra < R ? pos0 + ra / G : -1, pos_b = rb < R ? pos0 + rb / G : -1;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
+  float o[HD / 8][4];
+#pragma unroll
+  for (int j = 0; j < HD / 8; ++j)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o[j][i] = 0.0f;
+
+  for (int tile = tile_lo; tile <= tile_hi; ++tile) {
+    const int stage = (tile - tile_lo) & 1;
+    const uint32_t ks = kv0 + stage * 2 * KT * LDS * 2, vs = ks + KT * LDS * 2;
+    if (tile < tile_hi) {
+      const uint32_t nk = kv0 + (stage ^ 1) * 2 * KT * LDS * 2;
+      load_kv_tile(nk, nk + KT * LDS * 2, p.cache, pages[tile + 1], p.n_kv_heads, kvh, tid, 128);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    tile_step(qf, ks, vs, tile * KT, pos_a, pos_b, p.window, p.scale_log2, m, l, o, lane);
+    __syncthreads();
+  }
+
+  const int t4 = lane & 3;
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+  }
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int r = half ? rb : ra;
+    if (r >= R) continue;
+    const float inv = 1.0f / l[half];
+    bf16* dst = p.out + ((size_t)(row0 + r / G) * p.n_q_heads + kvh * G + r % G) * HD;
+#pragma unroll
+    for (int j = 0; j < HD / 8; ++j)
+      *reinterpret_cast<uint32_t*>(dst + j * 8 + 2 * t4) =
+          pack_bf16(o[j][half * 2] * inv, o[j][half * 2 + 1] * inv);
+  }
+}
+
+// -------------------------------------------------------------------------------- decode
+// Shared memory: Q [16][LDS] bf16, then per warp K and V tiles [64][LDS]; after the keys are
+// done the tiles' space is reused for the warps' partial outputs.
+constexpr int DECODE_SMEM = (DEC_ROWS + 4 * 2 * KT) * LDS * 2;
+constexpr int PART_STRIDE = HD + 2;    // floats per partial row: o[HD], m, l
+
+__global__ void __launch_bounds__(128) attn_decode_kernel(const AttnParams p) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  const uint32_t qs = (uint32_t)__cvta_generic_to_shared(smem);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  const int G = p.n_q_heads / p.n_kv_heads;
+  const int row0 = p.seq_row0[b], n_new = p.seq_row0[b + 1] - row0, pos0 = p.seq_pos0[b];
+  const int R = n_new * G;
+  const int p_hi = pos0 + n_new - 1;
+  const int key_lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+  const int split_lo = key_lo / (SPLIT_PAGES * KT), split_hi = p_hi / (SPLIT_PAGES * KT);
+  if (split < split_lo || split > split_hi) return;
+  const int32_t* pages = p.page_ids + p.page_off[b];
+  const int tile = split * SPLIT_PAGES + warp;
+  const bool has_tile = tile >= key_lo / KT && tile <= p_hi / KT;
+
+  for (int idx = tid; idx < DEC_ROWS * (HD / 8); idx += 128) {
+    const int row = idx / (HD / 8), ch = idx % (HD / 8);
+    const bool valid = row < R;
+    const int t = valid ? row / G : 0, g = valid ? row % G : 0;
+    cp_async16(qs + (uint32_t)(row * LDS + ch * 8) * 2,
+               p.q + ((size_t)(row0 + t) * p.n_q_heads + kvh * G + g) * HD + ch * 8, valid);
+  }
+  const uint32_t ks = qs + (DEC_ROWS + warp * 2 * KT) * LDS * 2, vs = ks + KT * LDS * 2;
+  if (has_tile) load_kv_tile(ks, vs, p.cache, pages[tile], p.n_kv_heads, kvh, lane, 32);
+  cp_async_commit();
+  cp_async_wait<0>();
+  __syncthreads();
+
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
+  float o[HD / 8][4];
+#pragma unroll
+  for (int j = 0; j < HD / 8; ++j)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o[j][i] = 0.0f;
+  const int ra = lane >> 2, rb = ra + 8;
+  if (has_tile) {
+    uint32_t qf[HD / 16][4];
+    load_q_frags(qs, 0, lane, qf);
+    const int pos_a = ra < R ? pos0 + ra / G : -1, pos_b = rb < R ? pos0 + rb / G : -1;
+    tile_step(qf, ks, vs, tile * KT, pos_a, pos_b, p.window, p.scale_log2, m, l, o, lane);
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+  }
+  __syncthreads();                                   // every warp is done with its tiles
+  float* part = reinterpret_cast<float*>(smem + DEC_ROWS * LDS * 2);   // [warp][16][PART_STRIDE]
+  const int t4 = lane & 3;
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    float* dst = part + ((size_t)warp * DEC_ROWS + (half ? rb : ra)) * PART_STRIDE;
+#pragma unroll
+    for (int j = 0; j < HD / 8; ++j) {
+      dst[j * 8 + 2 * t4] = o[j][half * 2];
+      dst[j * 8 + 2 * t4 + 1] = o[j][half * 2 + 1];
+    }
+    if (t4 == 0) {
+      dst[HD] = m[half];
+      dst[HD + 1] = l[half];
+    }
+  }
+  __syncthreads();
+  // merge the four warps in warp order: thread handles (row, d) pairs
+  const bool single = split_lo == split_hi;
+  for (int idx = tid; idx < R * HD; idx += 128) {
+    const int row = idx / HD, d = idx % HD;
+    float mm = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) mm = fmaxf(mm, part[((size_t)w * DEC_ROWS + row) * PART_STRIDE + HD]);
+    const float base = mm == -INFINITY ? 0.0f : mm;
+    float acc = 0.0f, ll = 0.0f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float* src = part + ((size_t)w * DEC_ROWS + row) * PART_STRIDE;
+      const float f = exp2f(src[HD] - base);
+      acc += src[d] * f;
+      ll += src[HD + 1] * f;
+    }
+    const int tok = row / G, g = row % G;
+    if (single) {
+      p.out[((size_t)(row0 + tok) * p.n_q_heads + kvh * G + g) * HD + d] = __float2bfloat16_rn(acc / ll);
+    } else {
+      // scratch: [row of the batch][query head][split][HD + 2]
+      float* dst = p.scratch +
+                   (((size_t)(row0 + tok) * p.n_q_heads + kvh * G + g) * p.n_splits + split) * PART_STRIDE;
+      dst[d] = acc;
+      if (d == 0) {
+        dst[HD] = mm;
+        dst[HD + 1] = ll;
+      }
+    }
+  }
+}
+
+// Merges a row's splits in ascending order.  Grid: (rows, query heads).
+__global__ void __launch_bounds__(128)
+attn_merge_kernel(const AttnParams p, const int32_t* __restrict__ row_seq_unused, int n_rows) {
+  const int row = blockIdx.x, head = blockIdx.y;
+  // find the sequence of this row by its row range (few sequences; linear scan by one thread)
+  __shared__ int s_lo, s_hi;
+  if (threadIdx.x == 0) {
+    int b = 0;
+    while (p.seq_row0[b + 1] <= row) ++b;
+    const int pos0 = p.seq_pos0[b], n_new = p.seq_row0[b + 1] - p.seq_row0[b];
+    const int key_lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+    s_lo = key_lo / (SPLIT_PAGES * KT);
+    s_hi = (pos0 + n_new - 1) / (SPLIT_PAGES * KT);
+  }
+  __syncthreads();
+  const int lo = s_lo, hi = s_hi;
+  if (lo == hi) return;                              // the decode kernel wrote the output itself
+  const float* base = p.scratch + ((size_t)row * p.n_q_heads + head) * p.n_splits * PART_STRIDE;
+  float mm = -INFINITY;
+  for (int s = lo; s <= hi; ++s) mm = fmaxf(mm, base[(size_t)s * PART_STRIDE + HD]);
+  const float ref = mm == -INFINITY ? 0.0f : mm;
+  for (int d = threadIdx.x; d < HD; d += 128) {
+    float acc = 0.0f, ll = 0.0f;
+    for (int s = lo; s <= hi; ++s) {
+      const float* src = base + (size_t)s * PART_STRIDE;
+      const float f = exp2f(src[HD] - ref);
+      acc += src[d] * f;
+      ll += src[HD + 1] * f;
+    }
+    p.out[((size_t)row * p.n_q_heads + head) * HD + d] = __float2bfloat16_rn(acc / ll);
+  }
+}
+
+int n_splits_for(int max_len) { return (max_len + SPLIT_PAGES * KT - 1) / (SPLIT_PAGES * KT); }
+
+}  // namespace
+
+extern "C" int sb_attention_head_dim() { return HD; }
+
+// Bytes of scratch sb_attention needs for a step with these bounds (0 when none is used).
+extern "C" size_t sb_attention_scratch_bytes(int n_rows, int n_q_heads, int n_kv_heads, int max_new,
+                                             int max_len) {
+  const int G = n_q_heads / (n_kv_heads > 0 ? n_kv_heads : 1);
+  if (max_new * G > DEC_ROWS) return 0;
+  const int n_splits = n_splits_for(max_len);
+  if (n_splits <= 1) return 0;
+  return (size_t)n_rows * n_q_heads * n_splits * PART_STRIDE * sizeof(float);
+}
+
+// q [rows, heads, HD] and out [rows, heads*HD] bfloat16; cache: one schedule entry's pages,
+// bfloat16; max_new / max_len: upper bounds of new rows per sequence and of any sequence's
+// length after this step (they size the grid; the true values are read on the device).
+extern "C" int sb_attention(const void* q, void* out, int n_rows, int n_seqs, int max_new,
+                            const int32_t* seq_row0, const int32_t* seq_pos0,
+                            const int32_t* page_off, const int32_t* page_ids, int page_size,
+                            const void* cache, int n_q_heads, int n_kv_heads, int hd, int window,
+                            float scale, void* scratch, size_t scratch_bytes, int max_len,
+                            cudaStream_t stream) {
+  if (hd != HD) SB_FAIL(SB_ERR_ARG, "sb_attention: built for head size %d, called with %d", HD, hd);
+  if (page_size != KT)
+    SB_FAIL(SB_ERR_UNSUPPORTED, "sb_attention: cache pages of %d keys (needs %d)", page_size, KT);
+  if (n_rows <= 0 || n_seqs <= 0 || max_new <= 0 || max_len <= 0 || n_q_heads <= 0 || n_kv_heads <= 0)
+    SB_FAIL(SB_ERR_ARG, "sb_attention: rows=%d seqs=%d max_new=%d max_len=%d heads=%d/%d", n_rows,
+            n_seqs, max_new, max_len, n_q_heads, n_kv_heads);
+  if (n_q_heads % n_kv_heads)
+    SB_FAIL(SB_ERR_ARG, "sb_attention: %d query heads are not a multiple of %d key/value heads",
+            n_q_heads, n_kv_heads);
+  if (n_kv_heads > 65535 || n_seqs > 65535)
+    SB_FAIL(SB_ERR_UNSUPPORTED, "sb_attention: %d key/value heads, %d sequences", n_kv_heads, n_seqs);
+  if (((uintptr_t)q | (uintptr_t)cache) & 15) SB_FAIL(SB_ERR_ARG, "sb_attention: unaligned operands");
+  AttnParams p;
+  p.q = (const bf16*)q; p.out = (bf16*)out;
+  p.seq_row0 = seq_row0; p.seq_pos0 = seq_pos0; p.page_off = page_off; p.page_ids = page_ids;
+  p.cache = (const bf16*)cache; p.scratch = (float*)scratch;
+  p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads; p.window = window;
+  p.scale_log2 = scale * LOG2E;
+  const int G = n_q_heads / n_kv_heads;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e1 = cudaFuncSetAttribute(attn_prefill_kernel,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, PREFILL_SMEM);
+    cudaError_t e2 = cudaFuncSetAttribute(attn_decode_kernel,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, DECODE_SMEM);
+    if (e1 != cudaSuccess || e2 != cudaSuccess)
+      SB_FAIL(SB_ERR_CUDA, "sb_attention: shared memory opt-in failed: %s",
+              cudaGetErrorString(e1 != cudaSuccess ? e1 : e2));
+    configured = true;
+  }
+  if (max_new * G <= DEC_ROWS) {
+    p.n_splits = n_splits_for(max_len);
+    const size_t need = sb_attention_scratch_bytes(n_rows, n_q_heads, n_kv_heads, max_new, max_len);
+    if (need > scratch_bytes || (need && !scratch))
+      SB_FAIL(SB_ERR_ARG, "sb_attention: %zu bytes of scratch needed, %zu given", need, scratch_bytes);
+    attn_decode_kernel<<<dim3(p.n_splits, n_kv_heads, n_seqs), 128, DECODE_SMEM, stream>>>(p);
+    SB_CHECK_LAUNCH("sb_attention (decode)");
+    if (p.n_splits > 1) {
+      if (n_q_heads > 65535) SB_FAIL(SB_ERR_UNSUPPORTED, "sb_attention: %d heads", n_q_heads);
+      attn_merge_kernel<<<dim3(n_rows, n_q_heads), 128, 0, stream>>>(p, nullptr, n_rows);
+      SB_CHECK_LAUNCH("sb_attention (merge)");
+    }
+    return SB_OK;
+  }
+  p.n_splits = 1;
+  const long tiles = ((long)max_new * G + BM - 1) / BM;
+  if (tiles > 2147483647L) SB_FAIL(SB_ERR_UNSUPPORTED, "sb_attention: too many rows");
+  attn_prefill_kernel<<<dim3((unsigned)tiles, n_kv_heads, n_seqs), 128, PREFILL_SMEM, stream>>>(p);
+  SB_CHECK_LAUNCH("sb_attention (prefill)");
+  return SB_OK;
+}

@@ -31,8 +31,16 @@ class BuildError(RuntimeError):
     pass
 
 
+# Sources that are compiled once per parameter value into libraries of their own, not into the
+# core library: {source: macro}.  The attention kernels are specialised by head size.
+VARIANT_SOURCES = {"attn_mma.cu": "SB_HD"}
+SHARED_SOURCES = ["error.cu"]            # linked into every library
+HEAD_DIMS = tuple(range(16, 257, 16))    # head sizes the attention kernels are written for
+
+
 def sources() -> list[Path]:
-    return sorted(SRC_DIR.glob("*.cu"))
+    """Sources of the core library."""
+    return [p for p in sorted(SRC_DIR.glob("*.cu")) if p.name not in VARIANT_SOURCES]
 
 
 def _nvcc() -> str:
@@ -43,12 +51,12 @@ def _nvcc() -> str:
                      "kernel library cannot be built and there is no other implementation")
 
 
-def _stamp() -> str:
+def _stamp(srcs, defines=()) -> str:
     h = hashlib.sha256()
-    for p in sources() + sorted(SRC_DIR.glob("*.cuh")) + sorted(SRC_DIR.glob("*.h")):
+    for p in list(srcs) + sorted(SRC_DIR.glob("*.cuh")) + sorted(SRC_DIR.glob("*.h")):
         h.update(p.name.encode())
         h.update(p.read_bytes())
-    h.update(" ".join(ARCH_FLAGS + NVCC_FLAGS).encode())
+    h.update(" ".join(ARCH_FLAGS + NVCC_FLAGS + list(defines)).encode())
     return h.hexdigest()
 
 
@@ -61,7 +69,7 @@ def _build_dir() -> Path:
         probe.unlink()
         return in_tree
     except OSError:
-        d = Path(tempfile.gettempdir()) / f"sonicboom_b200-{os.getuid()}-{_stamp()[:12]}"
+        d = Path(tempfile.gettempdir()) / f"sonicboom_b200-{os.getuid()}"
         d.mkdir(parents=True, exist_ok=True)
         return d
 
@@ -70,21 +78,22 @@ def _say(msg: str) -> None:
     print(f"[sonicboom_b200] {msg}", file=sys.stderr, flush=True)
 
 
-def build(force: bool = False, verbose: bool = True) -> Path:
-    """Compiles every .cu of this folder and links them; returns the library's path."""
+def _build_lib(lib_name: str, srcs, defines=(), force=False, verbose=True) -> Path:
     out_dir = _build_dir()
-    lib, stamp_file, stamp = out_dir / LIB_NAME, out_dir / "stamp", _stamp()
+    lib, stamp_file = out_dir / lib_name, out_dir / (lib_name + ".stamp")
+    stamp = _stamp(srcs, defines)
     if not force and lib.is_file() and stamp_file.is_file() and stamp_file.read_text() == stamp:
         return lib
     nvcc = _nvcc()
-    srcs = sources()
     t0 = time.time()
     if verbose:
-        _say(f"compiling {len(srcs)} CUDA files for sm_100a into {out_dir} (first use only)")
+        _say(f"compiling {lib_name} for sm_100a ({len(srcs)} CUDA files) into {out_dir}")
+    tag = lib_name.replace(".so", "")
 
     def compile_one(src: Path):
-        obj = out_dir / (src.stem + ".o")
-        cmd = [nvcc, *ARCH_FLAGS, *NVCC_FLAGS, "-I", str(SRC_DIR), "-c", str(src), "-o", str(obj)]
+        obj = out_dir / f"{tag}.{src.stem}.o"
+        cmd = [nvcc, *ARCH_FLAGS, *NVCC_FLAGS, *defines, "-I", str(SRC_DIR), "-c", str(src),
+               "-o", str(obj)]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if verbose:
             _say(f"  {src.name}: {'ok' if r.returncode == 0 else 'FAILED'} ({time.time() - t0:.0f}s)")
@@ -96,28 +105,61 @@ def build(force: bool = False, verbose: bool = True) -> Path:
             if r.returncode != 0:
                 raise BuildError(f"nvcc failed on {src.name}:\n{r.stdout}\n{r.stderr}")
             objs.append(str(obj))
-    tmp_lib = out_dir / (LIB_NAME + f".tmp{os.getpid()}")
+    tmp_lib = out_dir / (lib_name + f".tmp{os.getpid()}")
     r = subprocess.run([nvcc, *ARCH_FLAGS, "-shared", "-o", str(tmp_lib), *objs],
                        capture_output=True, text=True)
     if r.returncode != 0:
-        raise BuildError(f"linking {LIB_NAME} failed:\n{r.stdout}\n{r.stderr}")
+        raise BuildError(f"linking {lib_name} failed:\n{r.stdout}\n{r.stderr}")
     os.replace(tmp_lib, lib)
     stamp_file.write_text(stamp)
     if verbose:
-        _say(f"built {lib.name} in {time.time() - t0:.0f}s")
+        _say(f"built {lib_name} in {time.time() - t0:.0f}s")
     return lib
 
 
-_LIB = None
+def build(force: bool = False, verbose: bool = True) -> Path:
+    """Compiles the core library (every .cu that is not a variant source)."""
+    return _build_lib(LIB_NAME, sources(), (), force, verbose)
+
+
+def build_attention(head_dim: int, force: bool = False, verbose: bool = True) -> Path:
+    """Compiles the tensor-core attention kernels for one head size."""
+    if head_dim not in HEAD_DIMS:
+        raise BuildError(f"the tensor-core attention kernels take head sizes in steps of 16 up to "
+                         f"{HEAD_DIMS[-1]}, not {head_dim}")
+    srcs = [SRC_DIR / "attn_mma.cu"] + [SRC_DIR / s for s in SHARED_SOURCES]
+    return _build_lib(f"libsonicboom_b200_attn_hd{head_dim}.so", srcs, (f"-DSB_HD={head_dim}",),
+                      force, verbose)
+
+
+def build_all(force: bool = False, verbose: bool = True) -> list[Path]:
+    """Everything that can be compiled: the core library and attention for every head size."""
+    libs = [build(force, verbose)]
+    with ThreadPoolExecutor(max_workers=4) as pool:
+        libs += list(pool.map(lambda hd: build_attention(hd, force, verbose), HEAD_DIMS))
+    return libs
+
+
+_LIBS: dict = {}
+
+
+def _load(path: Path) -> ctypes.CDLL:
+    try:
+        return ctypes.CDLL(str(path))
+    except OSError as e:
+        raise BuildError(f"could not load {path}: {e}") from None
 
 
 def load() -> ctypes.CDLL:
-    """The loaded library; builds it first when needed."""
-    global _LIB
-    if _LIB is None:
-        path = build()
-        try:
-            _LIB = ctypes.CDLL(str(path))
-        except OSError as e:
-            raise BuildError(f"could not load {path}: {e}") from None
-    return _LIB
+    """The loaded core library; builds it first when needed."""
+    if "core" not in _LIBS:
+        _LIBS["core"] = _load(build())
+    return _LIBS["core"]
+
+
+def load_attention(head_dim: int) -> ctypes.CDLL:
+    """The loaded attention library of one head size; builds it first when needed."""
+    key = ("attn", head_dim)
+    if key not in _LIBS:
+        _LIBS[key] = _load(build_attention(head_dim))
+    return _LIBS[key]

@@ -1,19 +1,6 @@
 // Embedding gather, RMSNorm, dtype casts and the fused rotation + cache write.
 // Each kernel is templated on its storage types; arithmetic is float32 throughout.
-#include <stdarg.h>
-
 #include "common.cuh"
-
-static thread_local char g_error[512] = "";
-
-extern "C" const char* sb_last_error() { return g_error; }
-
-void sb_set_error(const char* fmt, ...) {
-  va_list ap;
-  va_start(ap, fmt);
-  vsnprintf(g_error, sizeof(g_error), fmt, ap);
-  va_end(ap);
-}
 
 extern "C" int sb_abi_version() { return 1; }
 

@@ -83,7 +83,7 @@ __device__ int block_argmax(float v, int id, float* sv, int* si) {
 __global__ void __launch_bounds__(THREADS)
 sample_kernel(float* logits, int vocab, const SbSampleParams* __restrict__ params,
               const int32_t* __restrict__ history, int history_stride,
-              int32_t* __restrict__ out_tokens) {
+              const int32_t* __restrict__ fed_pos, int32_t* __restrict__ out_tokens) {
   __shared__ int32_t h_tok[MAX_HISTORY];
   __shared__ float h_old[MAX_HISTORY];
   __shared__ uint32_t hist[256];
@@ -94,7 +94,9 @@ sample_kernel(float* logits, int vocab, const SbSampleParams* __restrict__ param
   __shared__ int s_keep;
 
   const int row = blockIdx.x, tid = threadIdx.x;
-  const SbSampleParams p = params[row];
+  SbSampleParams p = params[row];
+  // with `fed_pos`, the token produced follows the one fed at fed_pos[row] in this step
+  if (fed_pos) p.position = (uint64_t)fed_pos[row] + 1u;
   float* lg = logits + (size_t)row * vocab;
 
   // 1. penalties, in place (undone at the end).  h_tok[i] >= 0 marks a first occurrence.
@@ -288,22 +290,37 @@ sample_kernel(float* logits, int vocab, const SbSampleParams* __restrict__ param
   if (tid == 0) out_tokens[row] = result;
 }
 
+__global__ void add_kernel(int32_t* x, int n, int delta) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) x[i] += delta;
+}
+
 }  // namespace
+
+// x[i] += delta: advances the positions of a decode loop that stays on the device.
+extern "C" int sb_add_i32(int32_t* x, int n, int delta, cudaStream_t stream) {
+  if (n <= 0) SB_FAIL(SB_ERR_ARG, "sb_add_i32: n=%d", n);
+  add_kernel<<<(n + 255) / 256, 256, 0, stream>>>(x, n, delta);
+  SB_CHECK_LAUNCH("sb_add_i32");
+  return SB_OK;
+}
 
 extern "C" int sb_sample_params_size() { return (int)sizeof(SbSampleParams); }
 
 // logits [n_rows, vocab] float32 (penalties touch it in place and restore it); params: one
 // SbSampleParams per row in device memory; history [n_rows, history_stride] int32 (may be null
-// when no row has history); out_tokens int32 [n_rows].
+// when no row has history); fed_pos, when given, holds the position of the token each row was
+// fed in this step and overrides the records' `position` with fed_pos + 1 (a loop that runs
+// on the device advances it there); out_tokens int32 [n_rows].
 extern "C" int sb_sample(float* logits, int n_rows, int vocab, const void* params,
-                         const int32_t* history, int history_stride, int32_t* out_tokens,
-                         cudaStream_t stream) {
+                         const int32_t* history, int history_stride, const int32_t* fed_pos,
+                         int32_t* out_tokens, cudaStream_t stream) {
   if (n_rows <= 0 || vocab <= 0) SB_FAIL(SB_ERR_ARG, "sb_sample: n_rows=%d vocab=%d", n_rows, vocab);
   if (history_stride < 0 || history_stride > MAX_HISTORY)
     SB_FAIL(SB_ERR_UNSUPPORTED, "sb_sample: a penalty window of %d tokens is above the cap of %d",
             history_stride, MAX_HISTORY);
   sample_kernel<<<n_rows, THREADS, 0, stream>>>(logits, vocab, (const SbSampleParams*)params,
-                                                history, history_stride, out_tokens);
+                                                history, history_stride, fed_pos, out_tokens);
   SB_CHECK_LAUNCH("sb_sample");
   return SB_OK;
 }

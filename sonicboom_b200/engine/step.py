@@ -83,15 +83,14 @@ class StepPlan:
                        for gi in range(len(cache.groups))]
         self.host_row_pos = row_pos
         self._scratch = None
-        self.attn_scratch_bytes = 0
 
-    def attn_scratch(self, device):
-        """Scratch for the split attention kernel's partial results (made on first use)."""
-        if self._scratch is None:
-            from ..ops import attention_scratch_bytes
-            self.attn_scratch_bytes = attention_scratch_bytes(self)
-            self._scratch = torch.empty(max(self.attn_scratch_bytes, 16), dtype=torch.uint8,
-                                        device=device)
+    def scratch(self, nbytes: int, device):
+        """Scratch memory shared by the step's kernels (made on first use, grown on demand);
+        None when nothing is asked for."""
+        if nbytes <= 0:
+            return None
+        if self._scratch is None or self._scratch.numel() < nbytes:
+            self._scratch = torch.empty(nbytes, dtype=torch.uint8, device=device)
         return self._scratch
 
 

@@ -57,9 +57,14 @@ def _stream():
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
-def _check(rc: int, what: str) -> None:
+LAUNCHES = 0          # kernels launched through this module so far (a running count)
+
+
+def _check(rc: int, what: str, launches: int = 1) -> None:
+    global LAUNCHES
     if rc != 0:
         raise KernelError(f"{what}: {lib().sb_last_error().decode()}")
+    LAUNCHES += launches
 
 
 def _i32(t, what):
@@ -158,23 +163,49 @@ def rope_store(qkv: torch.Tensor, n_q_heads: int, n_kv_heads: int, head_dim: int
     return q_out
 
 
+_attn_libs: dict = {}
+
+
+def attention_lib(head_dim: int):
+    """The tensor-core attention library of one head size, or None when the head size is
+    outside what those kernels are written for (multiples of 16 up to 256)."""
+    if head_dim not in _attn_libs:
+        if head_dim in _build.HEAD_DIMS:
+            l = _build.load_attention(head_dim)
+            l.sb_last_error.restype = ctypes.c_char_p
+            l.sb_attention_scratch_bytes.restype = ctypes.c_size_t
+            _attn_libs[head_dim] = l
+        else:
+            _attn_libs[head_dim] = None
+    return _attn_libs[head_dim]
+
+
 def attention(q: torch.Tensor, out: torch.Tensor, plan, group_index: int, cache: torch.Tensor,
               n_q_heads: int, n_kv_heads: int, head_dim: int, window: int, scale: float,
               kernel: str = "auto") -> torch.Tensor:
-    """Causal grouped-query attention of the step's rows over one cache entry's pages."""
+    """Causal grouped-query attention of the step's rows over one cache entry's pages.
+
+    bfloat16 runs the tensor-core kernels (built for the head size at first use); float32, a
+    head size those kernels do not take, or `kernel="plain"` run the plain kernel."""
     n = q.shape[0]
     g = plan.groups[group_index]
-    l = lib()
-    fast = q.dtype == torch.bfloat16 and kernel != "plain" and hasattr(l, "sb_attention")
-    if fast:
-        _check(l.sb_attention(
+    al = attention_lib(head_dim) if (q.dtype == torch.bfloat16 and cache.dtype == torch.bfloat16
+                                     and kernel != "plain") else None
+    if al is not None:
+        need = int(al.sb_attention_scratch_bytes(n, n_q_heads, n_kv_heads, plan.max_new, plan.max_len))
+        scratch = plan.scratch(need, q.device)
+        rc = al.sb_attention(
             _ptr(q), _ptr(out), n, plan.n_seqs, plan.max_new, _i32(plan.seq_row0, "seq_row0"),
             _i32(plan.seq_pos0, "seq_pos0"), _i32(g.page_off, "page_off"),
             _i32(g.page_ids, "page_ids"), g.page_size, _ptr(cache), n_q_heads, n_kv_heads,
-            head_dim, window, ctypes.c_float(scale), _ptr(plan.attn_scratch(q.device)),
-            ctypes.c_size_t(plan.attn_scratch_bytes), plan.max_len, _stream()), "attention")
+            head_dim, window, ctypes.c_float(scale), _ptr(scratch),
+            ctypes.c_size_t(scratch.numel() if scratch is not None else 0), plan.max_len, _stream())
+        if rc != 0:
+            raise KernelError(f"attention: {al.sb_last_error().decode()}")
+        global LAUNCHES
+        LAUNCHES += 2 if need else 1
     else:
-        _check(l.sb_attention_plain(
+        _check(lib().sb_attention_plain(
             _ptr(q), _ptr(out), _code(q.dtype), n, _i32(plan.row_seq, "row_seq"),
             _i32(plan.row_pos, "row_pos"), _i32(g.page_off, "page_off"),
             _i32(g.page_ids, "page_ids"), g.page_size, _ptr(cache), _code(cache.dtype),
@@ -188,22 +219,21 @@ def sample_params_size() -> int:
 
 
 def sample(logits: torch.Tensor, params: torch.Tensor, history: torch.Tensor | None,
-           out_tokens: torch.Tensor) -> torch.Tensor:
-    """One token per logits row; `params` is a uint8 tensor of packed per-row records."""
+           out_tokens: torch.Tensor, fed_pos: torch.Tensor | None = None) -> torch.Tensor:
+    """One token per logits row; `params` is a uint8 tensor of packed per-row records.  With
+    `fed_pos` (int32 per row) the draw's position is fed_pos + 1 instead of the record's."""
     n, vocab = logits.shape
     assert logits.dtype == torch.float32 and params.dtype == torch.uint8
     assert params.numel() == n * sample_params_size()
     stride = history.shape[1] if history is not None else 0
     _check(lib().sb_sample(_ptr(logits), n, vocab, _ptr(params),
                            _i32(history, "history") if history is not None else _ptr(None),
-                           stride, _i32(out_tokens, "out_tokens"), _stream()), "sample")
+                           stride, _i32(fed_pos, "fed_pos") if fed_pos is not None else _ptr(None),
+                           _i32(out_tokens, "out_tokens"), _stream()), "sample")
     return out_tokens
 
 
-def attention_scratch_bytes(plan) -> int:
-    """Bytes of scratch the split attention kernel needs for this step's batch."""
-    l = lib()
-    if not hasattr(l, "sb_attention_scratch_bytes"):
-        return 0
-    l.sb_attention_scratch_bytes.restype = ctypes.c_size_t
-    return int(l.sb_attention_scratch_bytes(plan.n_seqs, plan.max_new, plan.max_len))
+def add_i32(x: torch.Tensor, delta: int) -> torch.Tensor:
+    """x += delta on the device (int32)."""
+    _check(lib().sb_add_i32(_i32(x, "x"), x.numel(), int(delta), _stream()), "add_i32")
+    return x
