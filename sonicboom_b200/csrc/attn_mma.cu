@@ -276,6 +276,9 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const AttnParams p) {
 // done the tiles' space is reused for the warps' partial outputs.
 constexpr int DECODE_SMEM = (DEC_ROWS + 4 * 2 * KT) * LDS * 2;
 constexpr int PART_STRIDE = HD + 2;    // floats per partial row: o[HD], m, l
+// The largest head sizes do not leave room for four warps' tiles in one block's shared memory
+// (227 KiB); their decode steps run through the prefill kernel instead.
+constexpr bool DECODE_FITS = DECODE_SMEM <= 227 * 1024;
 
 __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnParams p) {
   extern __shared__ __align__(128) unsigned char smem[];
@@ -416,7 +419,7 @@ extern "C" int sb_attention_head_dim() { return HD; }
 extern "C" size_t sb_attention_scratch_bytes(int n_rows, int n_q_heads, int n_kv_heads, int max_new,
                                              int max_len) {
   const int G = n_q_heads / (n_kv_heads > 0 ? n_kv_heads : 1);
-  if (max_new * G > DEC_ROWS) return 0;
+  if (max_new * G > DEC_ROWS || !DECODE_FITS) return 0;
   const int n_splits = n_splits_for(max_len);
   if (n_splits <= 1) return 0;
   return (size_t)n_rows * n_q_heads * n_splits * PART_STRIDE * sizeof(float);
@@ -454,14 +457,15 @@ extern "C" int sb_attention(const void* q, void* out, int n_rows, int n_seqs, in
   if (!configured) {
     cudaError_t e1 = cudaFuncSetAttribute(attn_prefill_kernel,
                                           cudaFuncAttributeMaxDynamicSharedMemorySize, PREFILL_SMEM);
-    cudaError_t e2 = cudaFuncSetAttribute(attn_decode_kernel,
-                                          cudaFuncAttributeMaxDynamicSharedMemorySize, DECODE_SMEM);
+    cudaError_t e2 = !DECODE_FITS ? cudaSuccess :
+        cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             DECODE_SMEM);
     if (e1 != cudaSuccess || e2 != cudaSuccess)
       SB_FAIL(SB_ERR_CUDA, "sb_attention: shared memory opt-in failed: %s",
               cudaGetErrorString(e1 != cudaSuccess ? e1 : e2));
     configured = true;
   }
-  if (max_new * G <= DEC_ROWS) {
+  if (max_new * G <= DEC_ROWS && DECODE_FITS) {
     p.n_splits = n_splits_for(max_len);
     const size_t need = sb_attention_scratch_bytes(n_rows, n_q_heads, n_kv_heads, max_new, max_len);
     if (need > scratch_bytes || (need && !scratch))
