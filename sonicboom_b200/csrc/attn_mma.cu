@@ -486,3 +486,82 @@ extern "C" int sb_attention(const void* q, void* out, int n_rows, int n_seqs, in
   SB_CHECK_LAUNCH("sb_attention (prefill)");
   return SB_OK;
 }
+
+// ------------------------------------------------------------------- no-allocation variant
+// See no_alloc.h: the split decode attention with its scratch in a fixed device array.
+#include "no_alloc.h"
+
+namespace {
+
+// In host code this name is only a handle for the runtime; it is not a device address.  The
+// address the kernels get comes from cudaGetSymbolAddress below.
+static __device__ __align__(256) unsigned char g_static_scratch[SB_STATIC_SCRATCH_BYTES];
+
+constexpr int MAX_DEVICES = 64;
+float* g_static_scratch_ptr[MAX_DEVICES] = {};     // per device, filled at that device's first call
+
+}  // namespace
+
+extern "C" size_t sb_attention_static_scratch_bytes(void) { return SB_STATIC_SCRATCH_BYTES; }
+
+extern "C" int sb_attention_decode_static(const void* q, void* out, int n_rows, int n_seqs,
+                                          int max_new, const int32_t* seq_row0,
+                                          const int32_t* seq_pos0, const int32_t* page_off,
+                                          const int32_t* page_ids, int page_size, const void* cache,
+                                          int n_q_heads, int n_kv_heads, int hd, int window,
+                                          float scale, int max_len, cudaStream_t stream) {
+  const char* who = "sb_attention_decode_static";
+  if (hd != HD) SB_FAIL(SB_ERR_ARG, "%s: built for head size %d, called with %d", who, HD, hd);
+  if (page_size != KT)
+    SB_FAIL(SB_ERR_UNSUPPORTED, "%s: cache pages of %d keys (needs %d)", who, page_size, KT);
+  if (n_rows <= 0 || n_seqs <= 0 || max_new <= 0 || max_len <= 0 || n_q_heads <= 0 ||
+      n_kv_heads <= 0 || n_q_heads % n_kv_heads)
+    SB_FAIL(SB_ERR_ARG, "%s: rows=%d seqs=%d max_new=%d max_len=%d heads=%d/%d", who, n_rows, n_seqs,
+            max_new, max_len, n_q_heads, n_kv_heads);
+  if (n_kv_heads > 65535 || n_seqs > 65535 || n_q_heads > 65535)
+    SB_FAIL(SB_ERR_UNSUPPORTED, "%s: %d/%d heads, %d sequences", who, n_q_heads, n_kv_heads, n_seqs);
+  if (((uintptr_t)q | (uintptr_t)cache) & 15) SB_FAIL(SB_ERR_ARG, "%s: unaligned operands", who);
+  const int G = n_q_heads / n_kv_heads;
+  if (max_new * G > DEC_ROWS || !DECODE_FITS)
+    SB_FAIL(SB_ERR_UNSUPPORTED,
+            "%s: decode steps only (%d new rows x %d heads per group is above %d rows, or the "
+            "head size is too large for the decode kernel)", who, max_new, G, DEC_ROWS);
+  const int n_splits = n_splits_for(max_len);
+  const size_t need = (size_t)n_rows * n_q_heads * n_splits * PART_STRIDE * sizeof(float);
+  if (need > SB_STATIC_SCRATCH_BYTES)
+    SB_FAIL(SB_ERR_UNSUPPORTED,
+            "%s: this step needs %zu bytes of scratch, the built-in array holds %u "
+            "(rows %d x heads %d x splits %d x %d floats)", who, need, SB_STATIC_SCRATCH_BYTES,
+            n_rows, n_q_heads, n_splits, PART_STRIDE);
+
+  int device = -1;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess || device < 0 || device >= MAX_DEVICES)
+    SB_FAIL(SB_ERR_CUDA, "%s: cudaGetDevice: %s (device %d)", who, cudaGetErrorString(e), device);
+  if (!g_static_scratch_ptr[device]) {
+    // set-up, once per device, with that device current
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+    if (e != cudaSuccess || !ptr)
+      SB_FAIL(SB_ERR_CUDA, "%s: cudaGetSymbolAddress: %s", who, cudaGetErrorString(e));
+    e = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             DECODE_SMEM);
+    if (e != cudaSuccess)
+      SB_FAIL(SB_ERR_CUDA, "%s: shared memory opt-in failed: %s", who, cudaGetErrorString(e));
+    g_static_scratch_ptr[device] = (float*)ptr;
+  }
+
+  AttnParams p;
+  p.q = (const bf16*)q; p.out = (bf16*)out;
+  p.seq_row0 = seq_row0; p.seq_pos0 = seq_pos0; p.page_off = page_off; p.page_ids = page_ids;
+  p.cache = (const bf16*)cache; p.scratch = g_static_scratch_ptr[device];
+  p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads; p.window = window; p.n_splits = n_splits;
+  p.scale_log2 = scale * LOG2E;
+  attn_decode_kernel<<<dim3(n_splits, n_kv_heads, n_seqs), 128, DECODE_SMEM, stream>>>(p);
+  SB_CHECK_LAUNCH("sb_attention_decode_static (decode)");
+  if (n_splits > 1) {
+    attn_merge_kernel<<<dim3(n_rows, n_q_heads), 128, 0, stream>>>(p, nullptr, n_rows);
+    SB_CHECK_LAUNCH("sb_attention_decode_static (merge)");
+  }
+  return SB_OK;
+}
