@@ -1,0 +1,512 @@
+// bfloat16 matrix product on the fifth-generation tensor cores: TMA-fed shared-memory ring,
+// tcgen05.mma issued by one thread with the accumulator in tensor memory, epilogue read back
+// with tcgen05.ld.  out[M,N] = A[M,K] . W[N,K]^T with the fused epilogues of gemm_plain.cu.
+//
+// One block computes a 128 x BN tile.  Warp 0 is the TMA producer, warp 1 allocates tensor
+// memory and issues the MMAs, warps 2-5 run the epilogue (one TMEM lane quarter each).  Both
+// operands are K-major; tiles are 64 values (128 bytes) wide in K and stored with the 128-byte
+// swizzle that the tensor maps write and the MMA descriptors read.  Rows and columns beyond
+// M, N and K are zero-filled by TMA, so any M and N and any K that is a multiple of 8 work.
+//
+// Two forms share the kernel:
+//   normal   A = activations (rows are tokens), B = weights: the prefill product;
+//   swapped  A = weights (128 weight rows per tile), B = activations (up to 64 rows): the
+//            decode product, which is bound by reading the weights once.  K may be split over
+//            several blocks; their partial tiles go to scratch memory and the block that
+//            arrives last adds them in split order and runs the epilogue, so the sum's order
+//            is fixed.
+//
+// Every wait on an mbarrier is bounded; when a bound is hit the kernel records a code in a
+// status word, stops issuing work and leaves normally (sb_tc5_status reads the word).
+#include <cuda.h>
+
+#include "common.cuh"
+
+int sb_check_linear_args(const char* who, int M, int N, int K, int epilogue, const void* bias,
+                         const float* residual, int out_dtype);
+
+namespace {
+
+typedef __nv_bfloat16 bf16;
+
+constexpr int BM = 128, BK = 64, UMMA_K = 16;
+constexpr int THREADS = 192;
+constexpr uint32_t WAIT_LIMIT = 1u << 22;
+
+__device__ int g_status = 0;          // 0 ok; else the code of the wait that gave up
+
+// ------------------------------------------------------------------------- PTX wrappers
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n.reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: false (and a status code) when the barrier did not flip in time.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int code) {
+  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (i > 4096) __nanosleep(128);
+  }
+  atomicCAS(&g_status, 0, code);
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, "
+      "{%2, %3}], [%4];\n" ::"r"(dst),
+      "l"(map), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(dst_smem),
+               "r"(cols));
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(taddr), "r"(cols));
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+}
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
+                                          uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
+        "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]),
+        "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]),
+        "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
+        "=r"(r[15])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile with the 128-byte swizzle: rows of 128
+// bytes, groups of 8 rows 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+  return (uint64_t)((addr & 0x3FFFFu) >> 4) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) |
+         (1ull << 46) | (2ull << 61);
+}
+// Instruction descriptor: float32 accumulator, bfloat16 A and B, both K-major, M = 128, N = bn.
+__host__ __device__ constexpr uint32_t instr_desc(int bn) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+template <typename TB>
+__device__ __forceinline__ float bias_at(const void* bias, int n) {
+  return sb_to_f32<TB>(((const TB*)bias)[n]);
+}
+
+struct Tc5Params {
+  int M, N, K;                 // the product's sizes as the caller sees them (rows, features, inner)
+  int epilogue, bias_dtype;
+  const void* bias;
+  const float* residual;
+  void* out;
+  int tiles_a, tiles_b;        // tiles along the A rows and along the B rows
+  int k_splits;                // swapped form: blocks that share one output tile
+  float* scratch;              // swapped form with k_splits > 1: [tile][split][BN][128] floats
+  int* counters;               // one per output tile, zero between launches
+};
+
+constexpr int stage_bytes(int bn) { return (BM + bn) * BK * 2; }
+constexpr int smem_bytes(int bn, int stages) { return stages * stage_bytes(bn) + 1024 + 256; }
+
+// ----------------------------------------------------------------------------- the kernel
+// SWAPPED = false: A rows are tokens (m), B rows are features (n).
+// SWAPPED = true:  A rows are features (n), B rows are tokens (m <= BN).
+template <int BN, int STAGES, bool SWAPPED, typename TO>
+__global__ void __launch_bounds__(THREADS)
+gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                const Tc5Params p) {
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t raw = (uint32_t)__cvta_generic_to_shared(smem_raw);
+  const uint32_t tiles = (raw + 1023u) & ~1023u;                       // 1024-byte aligned ring
+  const uint32_t bars = tiles + STAGES * stage_bytes(BN);
+  // full[s] at bars + 8 s, empty[s] at bars + 8 (STAGES + s), accumulator-full after them
+  const uint32_t full0 = bars, empty0 = bars + 8 * STAGES, acc_bar = bars + 16 * STAGES;
+  const uint32_t tmem_slot = acc_bar + 8;
+  volatile uint32_t* tmem_slot_ptr =
+      (volatile uint32_t*)(smem_raw + (tmem_slot - raw));
+  __shared__ int s_last;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // consecutive blocks walk the A tiles of one B tile (or K splits first, in the swapped form),
+  // so that a wave of blocks shares its operand tiles through L2
+  int tile_a, tile_b, split = 0;
+  if (SWAPPED) {
+    split = blockIdx.x % p.k_splits;
+    tile_a = blockIdx.x / p.k_splits;
+    tile_b = 0;
+  } else {
+    tile_a = blockIdx.x % p.tiles_a;
+    tile_b = blockIdx.x / p.tiles_a;
+  }
+  const int n_k_total = (p.K + BK - 1) / BK;
+  const int k_per = (n_k_total + p.k_splits - 1) / p.k_splits;
+  const int k_begin = split * k_per, k_end = min(n_k_total, k_begin + k_per);
+  const int n_k = max(0, k_end - k_begin);
+  constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full0 + 8 * s, 1);
+      mbar_init(empty0 + 8 * s, 1);
+    }
+    mbar_init(acc_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+
+  if (warp == 0 && lane == 0) {
+    // ---- producer
+    int issued = 0;
+    bool ok = true;
+    for (int i = 0; i < n_k && ok; ++i) {
+      const int s = i % STAGES;
+      ok = mbar_wait(empty0 + 8 * s, ((i / STAGES) & 1) ^ 1, 1);
+      if (!ok) break;
+      mbar_expect_tx(full0 + 8 * s, stage_bytes(BN));
+      const uint32_t a_dst = tiles + s * stage_bytes(BN), b_dst = a_dst + BM * BK * 2;
+      tma_load_2d(a_dst, &map_a, (k_begin + i) * BK, tile_a * BM, full0 + 8 * s);
+      tma_load_2d(b_dst, &map_b, (k_begin + i) * BK, tile_b * BN, full0 + 8 * s);
+      issued = i + 1;
+    }
+    if (!ok) {
+      // let copies that are still in flight land before the block's memory goes away
+      for (int i = max(0, issued - STAGES); i < issued; ++i)
+        mbar_wait(full0 + 8 * (i % STAGES), (i / STAGES) & 1, 2);
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ---- MMA issuer
+    constexpr uint32_t idesc = instr_desc(BN);
+    bool ok = true;
+    for (int i = 0; i < n_k && ok; ++i) {
+      const int s = i % STAGES;
+      ok = mbar_wait(full0 + 8 * s, (i / STAGES) & 1, 3);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t a_addr = tiles + s * stage_bytes(BN), b_addr = a_addr + BM * BK * 2;
+      const uint64_t adesc = smem_desc(a_addr), bdesc = smem_desc(b_addr);
+#pragma unroll
+      for (int k = 0; k < BK / UMMA_K; ++k)
+        umma_bf16(tmem_base, adesc + (uint64_t)(k * UMMA_K * 2 >> 4),
+                  bdesc + (uint64_t)(k * UMMA_K * 2 >> 4), idesc, (i > 0 || k > 0) ? 1u : 0u);
+      umma_commit(empty0 + 8 * s);          // the stage is free once these MMAs have read it
+    }
+    umma_commit(acc_bar);                   // arrives when every MMA above has finished
+  } else if (warp >= 2) {
+    // ---- epilogue: this warp reads TMEM lanes [32 q, 32 q + 32)
+    const int q = warp & 3;
+    const bool ok = mbar_wait(acc_bar, 0, 4);
+    tc_fence_after();
+    const int a_row = tile_a * BM + q * 32 + lane;            // this thread's row of A
+    const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16);
+    if (ok && n_k > 0) {
+      if (!SWAPPED) {
+        const int m = a_row;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld32(t_row + c * 32, r);
+          const int n0 = tile_b * BN + c * 32;
+          if (m >= p.M || n0 >= p.N) continue;
+          if (p.epilogue == SB_EPI_SWIGLU) {
+            TO* dst = (TO*)p.out + (size_t)m * (p.N / 2) + n0 / 2;
+#pragma unroll
+            for (int blk = 0; blk < 2; ++blk) {
+              if (n0 + blk * 16 >= p.N) break;
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                dst[blk * 8 + j] = sb_from_f32<TO>(sb_silu(__uint_as_float(r[blk * 16 + j])) *
+                                                   __uint_as_float(r[blk * 16 + 8 + j]));
+            }
+            continue;
+          }
+          TO* dst = (TO*)p.out + (size_t)m * p.N + n0;
+          const float* res = p.residual ? p.residual + (size_t)m * p.N + n0 : nullptr;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            if (n0 + j >= p.N) break;
+            float v = __uint_as_float(r[j]);
+            if (p.epilogue == SB_EPI_BIAS)
+              v += p.bias_dtype == SB_F32 ? bias_at<float>(p.bias, n0 + j) : bias_at<bf16>(p.bias, n0 + j);
+            else if (p.epilogue == SB_EPI_RESIDUAL)
+              v += res[j];
+            dst[j] = sb_from_f32<TO>(v);
+          }
+        }
+      } else {
+        // swapped: this thread owns feature n = a_row and holds its value for every token
+        const int n = a_row;
+        uint32_t r[32];
+        float acc[BN];
+#pragma unroll
+        for (int c = 0; c < (BN + 31) / 32; ++c) {
+          if (BN >= 32) tmem_ld32(t_row + c * 32, r); else tmem_ld16(t_row, r);
+#pragma unroll
+          for (int j = 0; j < (BN < 32 ? BN : 32); ++j) acc[c * 32 + j] = __uint_as_float(r[j]);
+        }
+        if (p.k_splits > 1) {
+          // partial tile to scratch: [tile][split][token][128 features]
+          float* dst = p.scratch + (((size_t)tile_a * p.k_splits + split) * BN) * BM + q * 32 + lane;
+#pragma unroll
+          for (int j = 0; j < BN; ++j)
+            if (j < p.M) dst[(size_t)j * BM] = acc[j];
+        } else {
+#pragma unroll
+          for (int j = 0; j < BN; ++j) {
+            if (j >= p.M) break;
+            float v = acc[j];
+            if (p.epilogue == SB_EPI_SWIGLU) {
+              const float up = __shfl_down_sync(0xffffffffu, v, 8);
+              if ((lane & 15) < 8 && n < p.N)
+                ((TO*)p.out)[(size_t)j * (p.N / 2) + (n >> 4) * 8 + (n & 7)] =
+                    sb_from_f32<TO>(sb_silu(v) * up);
+              continue;
+            }
+            if (n >= p.N) continue;
+            if (p.epilogue == SB_EPI_BIAS)
+              v += p.bias_dtype == SB_F32 ? bias_at<float>(p.bias, n) : bias_at<bf16>(p.bias, n);
+            else if (p.epilogue == SB_EPI_RESIDUAL)
+              v += p.residual[(size_t)j * p.N + n];
+            ((TO*)p.out)[(size_t)j * p.N + n] = sb_from_f32<TO>(v);
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+
+  if (SWAPPED && p.k_splits > 1) {
+    // The block that arrives last at this tile's counter adds the partial tiles in split order
+    // and runs the epilogue; the counter is left at zero for the next launch.
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const int seen = atomicAdd(&p.counters[tile_a], 1);
+      s_last = seen == p.k_splits - 1;
+      if (s_last) p.counters[tile_a] = 0;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    const float* base = p.scratch + (size_t)tile_a * p.k_splits * BN * BM;
+    for (int e = threadIdx.x; e < BM * BN; e += THREADS) {
+      const int f = e % BM, j = e / BM;                      // feature within the tile, token
+      if (j >= p.M) break;
+      const int n = tile_a * BM + f;
+      float v = 0.0f;
+      for (int s = 0; s < p.k_splits; ++s) v += base[((size_t)s * BN + j) * BM + f];
+      if (p.epilogue == SB_EPI_SWIGLU) {
+        if ((f & 15) >= 8 || n >= p.N) continue;
+        float up = 0.0f;
+        for (int s = 0; s < p.k_splits; ++s) up += base[((size_t)s * BN + j) * BM + f + 8];
+        ((TO*)p.out)[(size_t)j * (p.N / 2) + (n >> 4) * 8 + (n & 7)] = sb_from_f32<TO>(sb_silu(v) * up);
+        continue;
+      }
+      if (n >= p.N) continue;
+      if (p.epilogue == SB_EPI_BIAS)
+        v += p.bias_dtype == SB_F32 ? bias_at<float>(p.bias, n) : bias_at<bf16>(p.bias, n);
+      else if (p.epilogue == SB_EPI_RESIDUAL)
+        v += p.residual[(size_t)j * p.N + n];
+      ((TO*)p.out)[(size_t)j * p.N + n] = sb_from_f32<TO>(v);
+    }
+  }
+}
+
+// --------------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)ptr;
+  }
+  return fn;
+}
+
+// A [rows, K] bfloat16 row-major matrix as a tensor map with boxes of box_rows x 64.
+bool make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  const cuuint32_t elem[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
+            elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int BN, int STAGES, bool SWAPPED, typename TO>
+int launch(const CUtensorMap& ma, const CUtensorMap& mb, const Tc5Params& p, int blocks,
+           cudaStream_t stream) {
+  static bool configured = false;
+  constexpr int smem = smem_bytes(BN, STAGES);
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc5_kernel<BN, STAGES, SWAPPED, TO>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess)
+      SB_FAIL(SB_ERR_CUDA, "sb_gemm_tc5: shared memory opt-in failed: %s", cudaGetErrorString(e));
+    configured = true;
+  }
+  gemm_tc5_kernel<BN, STAGES, SWAPPED, TO><<<blocks, THREADS, smem, stream>>>(ma, mb, p);
+  SB_CHECK_LAUNCH("sb_gemm_tc5");
+  return SB_OK;
+}
+
+}  // namespace
+
+// 0 when no kernel has given up on a wait since the last call; else the code of the wait
+// (1 producer/empty, 2 producer drain, 3 MMA/full, 4 epilogue/accumulator).  Reading
+// synchronizes with the device.
+extern "C" int sb_tc5_status() {
+  int v = -1, zero = 0;
+  if (cudaMemcpyFromSymbol(&v, g_status, sizeof(int)) != cudaSuccess) return -1;
+  if (v != 0) cudaMemcpyToSymbol(g_status, &zero, sizeof(int));
+  return v;
+}
+
+namespace {
+
+int swapped_bn(int M) { return M <= 16 ? 16 : (M <= 32 ? 32 : 64); }
+
+// How many blocks share one output tile of the swapped form: enough to give every SM a block,
+// at least four K tiles each, and no block without work.
+int choose_splits(int N, int K, int n_sms) {
+  const int tiles = (N + BM - 1) / BM, n_k = (K + BK - 1) / BK;
+  int splits = n_sms > 0 ? n_sms / tiles : 1;
+  if (splits > 16) splits = 16;
+  if (splits > n_k / 4) splits = n_k / 4;
+  if (splits < 1) splits = 1;
+  const int k_per = (n_k + splits - 1) / splits;
+  return (n_k + k_per - 1) / k_per;
+}
+
+size_t counter_bytes(int tiles) { return ((size_t)tiles * sizeof(int) + 255) & ~(size_t)255; }
+
+}  // namespace
+
+// Bytes of scratch (tile counters + partial tiles) the swapped form needs for these sizes; 0
+// when K is not split.  The first counter_bytes must be zero before the first launch; the
+// kernel leaves them zero.
+extern "C" size_t sb_gemm_tc5_scratch_bytes(int M, int N, int K, int n_sms) {
+  if (M > 64 || M <= 0 || N <= 0 || K <= 0) return 0;
+  const int splits = choose_splits(N, K, n_sms);
+  if (splits <= 1) return 0;
+  const int tiles = (N + BM - 1) / BM;
+  return counter_bytes(tiles) + (size_t)tiles * splits * swapped_bn(M) * BM * sizeof(float);
+}
+
+extern "C" int sb_gemm_tc5(const void* A, int a_dtype, const void* W, int w_dtype, int M, int N,
+                           int K, int epilogue, const void* bias, int bias_dtype,
+                           const float* residual, void* out, int out_dtype, void* scratch,
+                           size_t scratch_bytes, int n_sms, cudaStream_t stream) {
+  if (int rc = sb_check_linear_args("sb_gemm_tc5", M, N, K, epilogue, bias, residual, out_dtype))
+    return rc;
+  if (a_dtype != SB_BF16 || w_dtype != SB_BF16)
+    SB_FAIL(SB_ERR_UNSUPPORTED, "sb_gemm_tc5: takes bfloat16 operands (got dtype codes %d, %d)",
+            a_dtype, w_dtype);
+  if (K % 8)
+    SB_FAIL(SB_ERR_UNSUPPORTED,
+            "sb_gemm_tc5: the inner size must be a multiple of 8 for 16-byte rows, got %d", K);
+  if (((uintptr_t)A | (uintptr_t)W) & 15) SB_FAIL(SB_ERR_ARG, "sb_gemm_tc5: operands must be 16-byte aligned");
+  if (!sb_valid_dtype(out_dtype)) SB_FAIL(SB_ERR_ARG, "sb_gemm_tc5: out dtype %d", out_dtype);
+
+  Tc5Params p;
+  p.M = M; p.N = N; p.K = K; p.epilogue = epilogue; p.bias = bias; p.bias_dtype = bias_dtype;
+  p.residual = residual; p.out = out; p.k_splits = 1; p.scratch = nullptr; p.counters = nullptr;
+  CUtensorMap ma, mb;
+  if (M > 64) {
+    constexpr int BN = 128;
+    p.tiles_a = (M + BM - 1) / BM;
+    p.tiles_b = (N + BN - 1) / BN;
+    if (!make_map(&ma, A, M, K, BM) || !make_map(&mb, W, N, K, BN))
+      SB_FAIL(SB_ERR_CUDA, "sb_gemm_tc5: cuTensorMapEncodeTiled failed");
+    const long blocks = (long)p.tiles_a * p.tiles_b;
+    if (blocks > 2147483647L) SB_FAIL(SB_ERR_UNSUPPORTED, "sb_gemm_tc5: too many tiles");
+    if (out_dtype == SB_F32) return launch<BN, 3, false, float>(ma, mb, p, (int)blocks, stream);
+    return launch<BN, 3, false, bf16>(ma, mb, p, (int)blocks, stream);
+  }
+  // swapped form: weights are the A operand
+  const int bn = swapped_bn(M);
+  p.tiles_a = (N + BM - 1) / BM;
+  p.tiles_b = 1;
+  const int splits = choose_splits(N, K, n_sms);
+  p.k_splits = splits;
+  if (splits > 1) {
+    const size_t need = sb_gemm_tc5_scratch_bytes(M, N, K, n_sms);
+    if (!scratch || scratch_bytes < need)
+      SB_FAIL(SB_ERR_ARG, "sb_gemm_tc5: %zu bytes of scratch needed, %zu given", need, scratch_bytes);
+    if ((uintptr_t)scratch & 255) SB_FAIL(SB_ERR_ARG, "sb_gemm_tc5: scratch must be 256-byte aligned");
+    p.counters = (int*)scratch;                      // kept at zero by the kernel itself
+    p.scratch = (float*)((char*)scratch + counter_bytes(p.tiles_a));
+  }
+  if (!make_map(&ma, W, N, K, BM) || !make_map(&mb, A, M, K, bn))
+    SB_FAIL(SB_ERR_CUDA, "sb_gemm_tc5: cuTensorMapEncodeTiled failed");
+  const int blocks = p.tiles_a * splits;
+#define SB_TC5_SWAPPED(BN_)                                                                  \
+  if (out_dtype == SB_F32) return launch<BN_, 6, true, float>(ma, mb, p, blocks, stream);     \
+  return launch<BN_, 6, true, bf16>(ma, mb, p, blocks, stream);
+  if (bn == 16) { SB_TC5_SWAPPED(16) }
+  if (bn == 32) { SB_TC5_SWAPPED(32) }
+  SB_TC5_SWAPPED(64)
+#undef SB_TC5_SWAPPED
+}

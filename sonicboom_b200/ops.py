@@ -131,16 +131,59 @@ def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = 
         assert residual.dtype == torch.float32 and tuple(residual.shape) == (M, N)
     if bias is not None:
         assert bias.numel() == N
-    fast = a.dtype == torch.bfloat16 and kernel != "plain"
+    fast = a.dtype == torch.bfloat16 and kernel != "plain" and K % 8 == 0
     l = lib()
-    if fast and (kernel == "skinny" or (kernel == "auto" and M <= SKINNY_MAX_ROWS)) \
-            and hasattr(l, "sb_gemm_skinny"):
+    if kernel == "auto" and fast:
+        kernel = AUTO_SKINNY if M <= SKINNY_MAX_ROWS else AUTO_WIDE
+    if fast and kernel == "tc5":
+        ws = _tc5_workspace(M, N, K, a.device)
+        _check(l.sb_gemm_tc5(*args[:-1], _ptr(ws), ctypes.c_size_t(ws.numel() if ws is not None else 0),
+                             _sm_count(a.device), _stream()), "linear (tcgen05 kernel)")
+    elif fast and kernel == "skinny":
         _check(l.sb_gemm_skinny(*args), "linear (weight-streaming kernel)")
-    elif fast and hasattr(l, "sb_gemm_tiled"):
+    elif fast and kernel == "tiled":
         _check(l.sb_gemm_tiled(*args), "linear (tiled kernel)")
-    else:
+    elif kernel in ("plain", "auto") or not fast:
         _check(l.sb_gemm_plain(*args), "linear (plain kernel)")
+    else:
+        raise KernelError(f"linear: unknown kernel {kernel!r}")
     return out
+
+
+# Which bfloat16 product kernel "auto" picks for few rows (decode) and for many (prefill).
+AUTO_SKINNY = "skinny"
+AUTO_WIDE = "tiled"
+
+_sm_counts: dict = {}
+_tc5_buffers: dict = {}          # device -> list of zero-initialised workspaces (never freed:
+                                 # captured graphs may hold their addresses)
+
+
+def _sm_count(device) -> int:
+    key = torch.device(device).index or 0
+    if key not in _sm_counts:
+        _sm_counts[key] = torch.cuda.get_device_properties(key).multi_processor_count
+    return _sm_counts[key]
+
+
+def _tc5_workspace(M: int, N: int, K: int, device):
+    """Workspace of the split-K decode product: tile counters (zero between launches) and
+    partial tiles.  One buffer per device serves every call on the stream; it only grows."""
+    l = lib()
+    l.sb_gemm_tc5_scratch_bytes.restype = ctypes.c_size_t
+    need = int(l.sb_gemm_tc5_scratch_bytes(M, N, K, _sm_count(device)))
+    if need == 0:
+        return None
+    key = torch.device(device).index or 0
+    bufs = _tc5_buffers.setdefault(key, [])
+    if not bufs or bufs[-1].numel() < need:
+        bufs.append(torch.zeros(max(need, 8 << 20), dtype=torch.uint8, device=device))
+    return bufs[-1]
+
+
+def tc5_status() -> int:
+    """0 unless a tcgen05 kernel gave up on a bounded wait since the last call (synchronizes)."""
+    return int(lib().sb_tc5_status())
 
 
 def rope_store(qkv: torch.Tensor, n_q_heads: int, n_kv_heads: int, head_dim: int, rotary_dim: int,
