@@ -131,7 +131,7 @@ def run(args) -> int:
     import torch
     import sonicboom_b200 as sb
     from sonicboom_b200.engine.decode import DecodeLoop
-    from sonicboom_b200 import ops
+    from sonicboom_b200 import llm, ops
 
     torch.cuda.set_device(0)
     dev = "cuda:0"
@@ -153,8 +153,9 @@ def run(args) -> int:
         return [torch.randint(0, cfg["vocab_size"], (PROMPT_LEN,), generator=gen).tolist()
                 for _ in range(n)]
 
-    def decode_point(batch, steps, warmup, e2e=False, clocks=None):
-        """Prefills `batch` prompts (8 at a time), then times `steps` decode steps."""
+    def decode_point(batch, steps, warmup, clocks=None):
+        """Prefills `batch` prompts (8 at a time), then times `steps` steps of the decode loop
+        on the device with CUDA events."""
         engine = sb.Engine(model, max_tokens=batch * CONTEXT, n_slots=batch)
         slots = [engine.open() for _ in range(batch)]
         ps = prompts(batch)
@@ -163,40 +164,47 @@ def run(args) -> int:
             lg = engine.step([(s, p, [len(p) - 1]) for s, p in zip(slots[i:i + 8], ps[i:i + 8])])
             first += lg.argmax(dim=-1).tolist()
         loop = DecodeLoop(engine, slots, max_new=min(CONTEXT - PROMPT_LEN, warmup + steps + 2))
-        ops.LAUNCHES = 0
-        if e2e:
-            tokens = loop.run_host(first, warmup)
-            torch.cuda.synchronize()
-            ctx_start = engine.length(slots[0])
-            t = time.perf_counter()
-            tokens = loop.run_host(tokens, steps)
-            torch.cuda.synchronize()
-            ms = (time.perf_counter() - t) * 1e3
-            launches = loop.launches_per_step * steps
-        else:
-            loop.run_device(first, warmup)
-            torch.cuda.synchronize()
-            ctx_start = engine.length(slots[0])
-            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            if clocks is not None:
-                clocks.__enter__()
-            start.record()
-            loop.run_device(None, steps)
-            end.record()
-            torch.cuda.synchronize()
-            if clocks is not None:
-                clocks.__exit__()
-            ms = start.elapsed_time(end)
-            launches = loop.launches_per_step * steps
-        ctx_mid = ctx_start + steps / 2.0
+        loop.run_device(first, warmup)
+        torch.cuda.synchronize()
+        ctx_start = engine.length(slots[0]) + warmup
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if clocks is not None:
+            clocks.__enter__()
+        start.record()
+        loop.run_device(None, steps)
+        end.record()
+        torch.cuda.synchronize()
+        if clocks is not None:
+            clocks.__exit__()
+        ms = start.elapsed_time(end)
+        launches = loop.launches_per_step * steps
         loop.close()
         for s in slots:
             engine.close(s)
-        del engine
+        del engine, loop
         torch.cuda.empty_cache()
         return {"tok_s": batch * steps / (ms / 1e3), "ms_per_step": ms / steps, "launches": launches,
-                "bytes_per_step": wbytes + batch * ctx_mid * kv_bytes_per_token,
-                "h2d": loop.h2d_bytes_per_step, "d2h": loop.d2h_bytes_per_step}
+                "bytes_per_step": wbytes + batch * (ctx_start + steps / 2.0) * kv_bytes_per_token}
+
+    def e2e_point(batch, steps, warmup):
+        """The same through the Python entry point: host token ids in, host token ids out.
+        generate_batch prefills the prompts and runs the decode loop; every step copies the
+        step's ids from pinned host memory and reads the new ids back.  The time between
+        the callbacks of token `warmup` and token `warmup + steps` is what is reported."""
+        engine = sb.Engine(model, max_tokens=batch * CONTEXT, n_slots=batch)
+        stamps = []
+
+        def on_token(i, tok):
+            if i == 0:
+                stamps.append(time.perf_counter())
+            return 0
+        outs = llm.generate_batch(llm.Model(model), prompts(batch), max_tokens=warmup + steps + 1,
+                                  ignore_eos=True, engine=engine, on_token=on_token, max_batch=batch)
+        assert all(len(o) == warmup + steps + 1 for o in outs)
+        dt = stamps[warmup + steps] - stamps[warmup]
+        del engine
+        torch.cuda.empty_cache()
+        return {"tok_s": batch * steps / dt, "h2d": 4 * batch, "d2h": 4 * batch}
 
     # prefill of one 2,048-token prompt
     engine = sb.Engine(model, max_tokens=PROMPT_LEN, n_slots=1)
@@ -221,7 +229,7 @@ def run(args) -> int:
 
     clocks = ClockSampler()
     main = decode_point(args.batch, args.steps, args.warmup, clocks=clocks)
-    e2e = decode_point(args.batch, args.steps, args.warmup, e2e=True)
+    e2e = e2e_point(args.batch, args.steps, args.warmup)
     points = {}
     for b in (1, 64):
         points[f"decode_b{b}"] = round(decode_point(b, args.steps, args.warmup)["tok_s"], 1)

@@ -12,8 +12,9 @@
 //
 //  * prefill kernel: 64 rows per block (4 warps x 16), key tiles of one cache page (64 keys)
 //    taken in ascending order with a double-buffered cp.async pipeline, online softmax.
-//  * decode kernel (at most 16 rows per sequence and head): the keys are cut into splits of 256
-//    at absolute positions; a block takes one split, each of its 4 warps one page of it; the
+//  * decode kernel (at most 16 rows per sequence and head): the keys are cut into splits of 128
+//    at absolute positions; a block takes one split, each of its 2 warps one page of it (small
+//    blocks, so that three of them fit an SM and their loads overlap each other's math); the
 //    warps' partial (m, l, o) are merged in warp order, and when a sequence has more than one
 //    split the blocks' partials go to scratch memory and a second kernel merges them in
 //    ascending order (core/src/model/emit.cpp:538-560 "chunk_index_asc",
@@ -38,7 +39,8 @@ constexpr int HD = SB_HD;
 constexpr int KT = 64;                 // keys per tile = cache page size
 constexpr int LDS = HD + 8;            // shared-memory row stride: an odd number of 16-byte chunks
 constexpr int BM = 64;                 // prefill rows per block
-constexpr int SPLIT_PAGES = 4;         // decode: pages per split (256 keys)
+constexpr int DEC_WARPS = 2;           // decode: warps per block, one cache page each
+constexpr int SPLIT_PAGES = DEC_WARPS; // decode: pages per split (128 keys)
 constexpr int DEC_ROWS = 16;
 constexpr float LOG2E = 1.4426950408889634f;
 
@@ -274,13 +276,13 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const AttnParams p) {
 // -------------------------------------------------------------------------------- decode
 // Shared memory: Q [16][LDS] bf16, then per warp K and V tiles [64][LDS]; after the keys are
 // done the tiles' space is reused for the warps' partial outputs.
-constexpr int DECODE_SMEM = (DEC_ROWS + 4 * 2 * KT) * LDS * 2;
+constexpr int DECODE_SMEM = (DEC_ROWS + DEC_WARPS * 2 * KT) * LDS * 2;
 constexpr int PART_STRIDE = HD + 2;    // floats per partial row: o[HD], m, l
-// The largest head sizes do not leave room for four warps' tiles in one block's shared memory
+// The largest head sizes do not leave room for the warps' tiles in one block's shared memory
 // (227 KiB); their decode steps run through the prefill kernel instead.
 constexpr bool DECODE_FITS = DECODE_SMEM <= 227 * 1024;
 
-__global__ void __launch_bounds__(128) attn_decode_kernel(const AttnParams p) {
+__global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(const AttnParams p) {
   extern __shared__ __align__(128) unsigned char smem[];
   const uint32_t qs = (uint32_t)__cvta_generic_to_shared(smem);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -296,7 +298,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnParams p) {
   const int tile = split * SPLIT_PAGES + warp;
   const bool has_tile = tile >= key_lo / KT && tile <= p_hi / KT;
 
-  for (int idx = tid; idx < DEC_ROWS * (HD / 8); idx += 128) {
+  for (int idx = tid; idx < DEC_ROWS * (HD / 8); idx += DEC_WARPS * 32) {
     const int row = idx / (HD / 8), ch = idx % (HD / 8);
     const bool valid = row < R;
     const int t = valid ? row / G : 0, g = valid ? row % G : 0;
@@ -344,17 +346,17 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnParams p) {
     }
   }
   __syncthreads();
-  // merge the four warps in warp order: thread handles (row, d) pairs
+  // merge the warps in warp order: thread handles (row, d) pairs
   const bool single = split_lo == split_hi;
-  for (int idx = tid; idx < R * HD; idx += 128) {
+  for (int idx = tid; idx < R * HD; idx += DEC_WARPS * 32) {
     const int row = idx / HD, d = idx % HD;
     float mm = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < 4; ++w) mm = fmaxf(mm, part[((size_t)w * DEC_ROWS + row) * PART_STRIDE + HD]);
+    for (int w = 0; w < DEC_WARPS; ++w) mm = fmaxf(mm, part[((size_t)w * DEC_ROWS + row) * PART_STRIDE + HD]);
     const float base = mm == -INFINITY ? 0.0f : mm;
     float acc = 0.0f, ll = 0.0f;
 #pragma unroll
-    for (int w = 0; w < 4; ++w) {
+    for (int w = 0; w < DEC_WARPS; ++w) {
       const float* src = part + ((size_t)w * DEC_ROWS + row) * PART_STRIDE;
       const float f = exp2f(src[HD] - base);
       acc += src[d] * f;
@@ -470,7 +472,7 @@ extern "C" int sb_attention(const void* q, void* out, int n_rows, int n_seqs, in
     const size_t need = sb_attention_scratch_bytes(n_rows, n_q_heads, n_kv_heads, max_new, max_len);
     if (need > scratch_bytes || (need && !scratch))
       SB_FAIL(SB_ERR_ARG, "sb_attention: %zu bytes of scratch needed, %zu given", need, scratch_bytes);
-    attn_decode_kernel<<<dim3(p.n_splits, n_kv_heads, n_seqs), 128, DECODE_SMEM, stream>>>(p);
+    attn_decode_kernel<<<dim3(p.n_splits, n_kv_heads, n_seqs), DEC_WARPS * 32, DECODE_SMEM, stream>>>(p);
     SB_CHECK_LAUNCH("sb_attention (decode)");
     if (p.n_splits > 1) {
       if (n_q_heads > 65535) SB_FAIL(SB_ERR_UNSUPPORTED, "sb_attention: %d heads", n_q_heads);
@@ -557,7 +559,7 @@ extern "C" int sb_attention_decode_static(const void* q, void* out, int n_rows, 
   p.cache = (const bf16*)cache; p.scratch = g_static_scratch_ptr[device];
   p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads; p.window = window; p.n_splits = n_splits;
   p.scale_log2 = scale * LOG2E;
-  attn_decode_kernel<<<dim3(n_splits, n_kv_heads, n_seqs), 128, DECODE_SMEM, stream>>>(p);
+  attn_decode_kernel<<<dim3(n_splits, n_kv_heads, n_seqs), DEC_WARPS * 32, DECODE_SMEM, stream>>>(p);
   SB_CHECK_LAUNCH("sb_attention_decode_static (decode)");
   if (n_splits > 1) {
     attn_merge_kernel<<<dim3(n_rows, n_q_heads), 128, 0, stream>>>(p, nullptr, n_rows);

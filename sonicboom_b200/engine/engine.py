@@ -15,6 +15,7 @@ class Engine:
 
     def __init__(self, model, max_tokens: int, n_slots: int | None = None):
         self.model = model
+        self.use_decode_loop = True
         self.cache = Cache(model.kv_needs(), model.state_needs(), max_tokens,
                            dtype=model.dtype, device=model.device, n_slots=n_slots)
 
@@ -39,6 +40,17 @@ class Engine:
 
     def free_slots(self) -> int:
         return self.cache.slots.free_count
+
+    def decode_loop(self, slots, max_new: int, samplings):
+        """The captured decode step for these live sequences, or None when it cannot serve
+        them: a windowed cache group gives pages back as it goes, and penalties need each
+        sequence's token history on the host."""
+        from .decode import DecodeLoop
+        if not self.use_decode_loop or any(g.need.window > 0 for g in self.cache.groups):
+            return None
+        if any(s.penalizes for s in samplings):
+            return None
+        return DecodeLoop(self, slots, max_new, samplings)
 
     def step(self, entries) -> torch.Tensor:
         """entries: StepEntry items or (slot, tokens, want) tuples."""

@@ -66,10 +66,9 @@ def run_batch(engine, sampler, batch: list, results: list, on_token: Optional[Ca
         live.append((r, engine.open(), list(r.prompt)))
     logits = engine.step([(slot, r.prompt, [len(r.prompt) - 1]) for r, slot, _ in live])
     steps = 1
+    tokens = sampler.sample(logits, [r.sampling for r, _, _ in live],
+                            [engine.length(slot) for _, slot, _ in live], [h for _, _, h in live])
     while True:
-        tokens = sampler.sample(logits, [r.sampling for r, _, _ in live],
-                                [engine.length(slot) for _, slot, _ in live],
-                                [h for _, _, h in live])
         still = []
         for (r, slot, hist), tok in zip(live, tokens):
             out = results[r.index]
@@ -85,8 +84,53 @@ def run_batch(engine, sampler, batch: list, results: list, on_token: Optional[Ca
         live = still
         if not live:
             return steps
+        make_loop = getattr(engine, "decode_loop", None)
+        loop = make_loop([slot for _, slot, _ in live],
+                         max(r.sampling.max_tokens - len(results[r.index]) for r, _, _ in live),
+                         [r.sampling for r, _, _ in live]) if make_loop else None
+        if loop is not None:
+            return steps + _run_device_loop(engine, loop, live, results, on_token)
         logits = engine.step([(slot, [hist[-1]], [0]) for _, slot, hist in live])
         steps += 1
+        tokens = sampler.sample(logits, [r.sampling for r, _, _ in live],
+                                [engine.length(slot) for _, slot, _ in live], [h for _, _, h in live])
+
+
+def _run_device_loop(engine, loop, live: list, results: list, on_token: Optional[Callable]) -> int:
+    """The rest of a batch on the engine's captured decode step: each step's token ids go in
+    from the host and the new ids come back.  A finished sequence stays in the captured batch
+    as a row nobody reads until fewer than half of the rows are live; then the step is captured
+    again for the live ones.  Finished sequences' slots are closed when that happens."""
+    steps = 0
+    rows = list(live)                            # the captured batch, in row order
+    done = [False] * len(rows)
+    while True:
+        new = loop.step_host([0 if d else hist[-1] for (_, _, hist), d in zip(rows, done)])
+        steps += 1
+        for i, ((r, slot, hist), tok) in enumerate(zip(rows, new)):
+            if done[i]:
+                continue
+            out = results[r.index]
+            out.append(tok)
+            hist.append(tok)
+            stop = tok in r.stop_tokens or len(out) >= r.sampling.max_tokens
+            if on_token is not None and on_token(r.index, tok):
+                stop = True
+            done[i] = stop
+        n_live = done.count(False)
+        if n_live == 0 or 2 * n_live <= len(rows):
+            loop.close()
+            for (r, slot, hist), d in zip(rows, done):
+                if d:
+                    engine.close(slot)
+            rows = [x for x, d in zip(rows, done) if not d]
+            if not rows:
+                return steps
+            done = [False] * len(rows)
+            loop = engine.decode_loop(
+                [slot for _, slot, _ in rows],
+                max(r.sampling.max_tokens - len(results[r.index]) for r, _, _ in rows),
+                [r.sampling for r, _, _ in rows])
 
 
 def _per_request_stops(stop_tokens, n: int) -> list:

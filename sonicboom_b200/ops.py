@@ -134,7 +134,7 @@ def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = 
     fast = a.dtype == torch.bfloat16 and kernel != "plain" and K % 8 == 0
     l = lib()
     if kernel == "auto" and fast:
-        kernel = AUTO_SKINNY if M <= SKINNY_MAX_ROWS else AUTO_WIDE
+        kernel = _pick_kernel(M, N, K, a.device)
     if fast and kernel == "tc5":
         ws = _tc5_workspace(M, N, K, a.device)
         _check(l.sb_gemm_tc5(*args[:-1], _ptr(ws), ctypes.c_size_t(ws.numel() if ws is not None else 0),
@@ -150,9 +150,19 @@ def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = 
     return out
 
 
-# Which bfloat16 product kernel "auto" picks for few rows (decode) and for many (prefill).
-AUTO_SKINNY = "skinny"
-AUTO_WIDE = "tiled"
+def _pick_kernel(M: int, N: int, K: int, device) -> str:
+    """Which bfloat16 product kernel "auto" means.  Above SKINNY_MAX_ROWS rows: the tcgen05
+    kernel.  Up to that many rows the product is bound by reading W once: the tcgen05 kernel
+    in its swapped form when W gives every SM a tile (or K is long and the rows are few),
+    else the kernel that streams W into mma.sync fragments, whose fixed costs are lower on
+    small matrices (measured on B200 at the 7B layer sizes)."""
+    if M > SKINNY_MAX_ROWS:
+        return "tc5"
+    tiles = (N + 127) // 128
+    if tiles >= _sm_count(device) or (K >= 8192 and M <= 32):
+        return "tc5"
+    return "skinny"
+
 
 _sm_counts: dict = {}
 _tc5_buffers: dict = {}          # device -> list of zero-initialised workspaces (never freed:

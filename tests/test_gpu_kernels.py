@@ -91,10 +91,12 @@ SHAPES = [(1, 24, 40), (3, 152, 72), (17, 1000, 200), (64, 96, 1024), (65, 264, 
 
 @pytest.mark.parametrize("M,N,K", SHAPES)
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("kernel", ["plain", "auto"])
+@pytest.mark.parametrize("kernel", ["plain", "auto", "skinny", "tiled", "tc5"])
 def test_linear_epilogues(M, N, K, dtype, kernel):
-    if dtype == "float32" and kernel == "auto":
+    if dtype == "float32" and kernel != "plain":
         pytest.skip("float32 has the plain kernel only")
+    if kernel == "skinny" and M > 64:
+        pytest.skip("the weight-streaming kernel takes at most 64 rows")
     dt = DT[dtype]
     a, w = rnd(M, K, dtype=dt), rnd(N, K, dtype=dt, scale=K ** -0.5, seed=1)
     bias, res = rnd(N, dtype=dt, seed=2), rnd(M, N, seed=3)
@@ -112,9 +114,10 @@ def test_linear_epilogues(M, N, K, dtype, kernel):
         if epi == ops.EPI_RESIDUAL:                 # in place on the residual stream
             ops.linear(a, w, r, epi, residual=r, kernel=kernel)
             assert torch.equal(r, out)
+    assert ops.tc5_status() == 0
 
 
-@pytest.mark.parametrize("kernel", ["plain", "auto"])
+@pytest.mark.parametrize("kernel", ["plain", "skinny", "tiled", "tc5"])
 def test_linear_rows_do_not_depend_on_the_batch(kernel):
     a, w = rnd(40, 256, dtype=torch.bfloat16), rnd(88, 256, dtype=torch.bfloat16, seed=1)
     full = torch.empty(40, 88, device=DEV)
