@@ -49,46 +49,52 @@ def peaks() -> dict:
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons while a timed region runs."""
-    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
-             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-             "clocks_event_reasons.sw_power_cap")
+    """Samples the SM clock and the throttle reasons (read-only NVML queries) every 50 ms while
+    a timed region runs."""
+    REASONS = {"sw_power_cap": 0x4, "hw_slowdown": 0x8, "sw_thermal_slowdown": 0x20,
+               "hw_thermal_slowdown": 0x40}
 
     def __init__(self):
-        self.samples, self._proc, self._thread = [], None, None
+        self.samples, self.max_mhz, self._stop, self._thread = [], None, None, None
 
     def __enter__(self):
         try:
-            self._proc = subprocess.Popen(
-                ["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self._thread = threading.Thread(target=self._read, daemon=True)
-            self._thread.start()
-        except OSError:
-            self._proc = None
+            import pynvml
+            pynvml.nvmlInit()
+            h = pynvml.nvmlDeviceGetHandleByIndex(0)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            return self
+        self._stop = threading.Event()
+
+        def poll():
+            while not self._stop.is_set():
+                try:
+                    mhz = int(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM))
+                    try:
+                        why = int(pynvml.nvmlDeviceGetCurrentClocksEventReasons(h))
+                    except Exception:
+                        why = int(pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(h))
+                    self.samples.append((mhz, why))
+                except Exception:
+                    pass
+                self._stop.wait(0.05)
+        self._thread = threading.Thread(target=poll, daemon=True)
+        self._thread.start()
         return self
 
-    def _read(self):
-        for line in self._proc.stdout:
-            parts = [x.strip() for x in line.split(",")]
-            if len(parts) == 6 and parts[0].isdigit():
-                self.samples.append(parts)
-
     def __exit__(self, *exc):
-        if self._proc is not None:
-            self._proc.terminate()
-            try:
-                self._proc.wait(timeout=5)
-            except subprocess.TimeoutExpired:
-                self._proc.kill()
+        if self._stop is not None:
+            self._stop.set()
+            self._thread.join(timeout=2)
 
     def summary(self) -> dict:
         if not self.samples:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
-        mhz = sorted(int(s[0]) for s in self.samples)
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for i, n in enumerate(names) if any(s[2 + i] == "Active" for s in self.samples)]
-        return {"sm_mhz": mhz[len(mhz) // 2], "sm_max_mhz": int(self.samples[0][1]), "reasons": reasons}
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": ["no samples"]}
+        mhz = sorted(m for m, _ in self.samples)
+        reasons = [n for n, bit in self.REASONS.items() if any(w & bit for _, w in self.samples)]
+        return {"sm_mhz": mhz[len(mhz) // 2], "sm_max_mhz": self.max_mhz, "reasons": reasons,
+                "samples": len(self.samples)}
 
 
 def reference_arm() -> int:
@@ -163,7 +169,16 @@ def run(args) -> int:
         for i in range(0, batch, 8):
             lg = engine.step([(s, p, [len(p) - 1]) for s, p in zip(slots[i:i + 8], ps[i:i + 8])])
             first += lg.argmax(dim=-1).tolist()
-        loop = DecodeLoop(engine, slots, max_new=min(CONTEXT - PROMPT_LEN, warmup + steps + 2))
+        # The sequences decode from 2,048 to 4,096 positions; the timed steps are the ones
+        # around the middle of that stretch.  Instead of decoding every token up to there, the
+        # sequences' lengths are moved forward (the skipped positions hold zeros in the cache;
+        # a step reads the same bytes either way).
+        skip = max(0, (CONTEXT + PROMPT_LEN) // 2 - (warmup + steps) // 2 - PROMPT_LEN)
+        skip = min(skip, CONTEXT - PROMPT_LEN - (warmup + steps + 2))
+        for s in slots:
+            engine.cache.reserve(s, PROMPT_LEN + skip)
+            engine.cache.advance(s, PROMPT_LEN + skip)
+        loop = DecodeLoop(engine, slots, max_new=warmup + steps + 2)
         loop.run_device(first, warmup)
         torch.cuda.synchronize()
         ctx_start = engine.length(slots[0]) + warmup
@@ -198,10 +213,12 @@ def run(args) -> int:
             if i == 0:
                 stamps.append(time.perf_counter())
             return 0
-        outs = llm.generate_batch(llm.Model(model), prompts(batch), max_tokens=warmup + steps + 1,
+        # decode from 2,048 up to the same stretch around position 3072 that `value` times
+        first = (CONTEXT - PROMPT_LEN) // 2 - steps // 2
+        outs = llm.generate_batch(llm.Model(model), prompts(batch), max_tokens=first + steps + 1,
                                   ignore_eos=True, engine=engine, on_token=on_token, max_batch=batch)
-        assert all(len(o) == warmup + steps + 1 for o in outs)
-        dt = stamps[warmup + steps] - stamps[warmup]
+        assert all(len(o) == first + steps + 1 for o in outs)
+        dt = stamps[first + steps] - stamps[first]
         del engine
         torch.cuda.empty_cache()
         return {"tok_s": batch * steps / dt, "h2d": 4 * batch, "d2h": 4 * batch}
@@ -246,6 +263,7 @@ def run(args) -> int:
                    "head_dim": hd, "intermediate": cfg["intermediate_size"],
                    "vocab": cfg["vocab_size"], "global_batch": args.batch, "seq_len": CONTEXT,
                    "prompt_len": PROMPT_LEN, "parallelism": "none (1 GPU)",
+                   "decode_positions": "timed steps centred on position 3072 of 2048..4096",
                    "l2": "inputs larger than L2 (weights read once per step)",
                    "peaks": pk["source"]},
         "e2e": {"value": round(e2e["tok_s"], 1), "unit": "tok/s",
@@ -267,7 +285,7 @@ def run(args) -> int:
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
