@@ -203,6 +203,8 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const AttnParams p) {
   extern __shared__ __align__(128) unsigned char smem[];
   const uint32_t qs = (uint32_t)__cvta_generic_to_shared(smem);
   const uint32_t kv0 = qs + BM * LDS * 2;                     // K0, V0, K1, V1
+  sb_pdl_launch();
+  sb_pdl_wait();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int b = blockIdx.z, kvh = blockIdx.y;
   const int G = p.n_q_heads / p.n_kv_heads;
@@ -285,6 +287,8 @@ constexpr bool DECODE_FITS = DECODE_SMEM <= 227 * 1024;
 __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(const AttnParams p) {
   extern __shared__ __align__(128) unsigned char smem[];
   const uint32_t qs = (uint32_t)__cvta_generic_to_shared(smem);
+  sb_pdl_launch();
+  sb_pdl_wait();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int G = p.n_q_heads / p.n_kv_heads;
@@ -384,6 +388,8 @@ attn_merge_kernel(const AttnParams p, const int32_t* __restrict__ row_seq_unused
   const int row = blockIdx.x, head = blockIdx.y;
   // find the sequence of this row by its row range (few sequences; linear scan by one thread)
   __shared__ int s_lo, s_hi;
+  sb_pdl_launch();
+  sb_pdl_wait();
   if (threadIdx.x == 0) {
     int b = 0;
     while (p.seq_row0[b + 1] <= row) ++b;
@@ -472,11 +478,13 @@ extern "C" int sb_attention(const void* q, void* out, int n_rows, int n_seqs, in
     const size_t need = sb_attention_scratch_bytes(n_rows, n_q_heads, n_kv_heads, max_new, max_len);
     if (need > scratch_bytes || (need && !scratch))
       SB_FAIL(SB_ERR_ARG, "sb_attention: %zu bytes of scratch needed, %zu given", need, scratch_bytes);
-    attn_decode_kernel<<<dim3(p.n_splits, n_kv_heads, n_seqs), DEC_WARPS * 32, DECODE_SMEM, stream>>>(p);
+    sb_launch(attn_decode_kernel, dim3(p.n_splits, n_kv_heads, n_seqs), dim3(DEC_WARPS * 32),
+              DECODE_SMEM, stream, p);
     SB_CHECK_LAUNCH("sb_attention (decode)");
     if (p.n_splits > 1) {
       if (n_q_heads > 65535) SB_FAIL(SB_ERR_UNSUPPORTED, "sb_attention: %d heads", n_q_heads);
-      attn_merge_kernel<<<dim3(n_rows, n_q_heads), 128, 0, stream>>>(p, nullptr, n_rows);
+      sb_launch(attn_merge_kernel, dim3(n_rows, n_q_heads), dim3(128), 0, stream, p,
+                (const int32_t*)nullptr, n_rows);
       SB_CHECK_LAUNCH("sb_attention (merge)");
     }
     return SB_OK;
@@ -484,7 +492,8 @@ extern "C" int sb_attention(const void* q, void* out, int n_rows, int n_seqs, in
   p.n_splits = 1;
   const long tiles = ((long)max_new * G + BM - 1) / BM;
   if (tiles > 2147483647L) SB_FAIL(SB_ERR_UNSUPPORTED, "sb_attention: too many rows");
-  attn_prefill_kernel<<<dim3((unsigned)tiles, n_kv_heads, n_seqs), 128, PREFILL_SMEM, stream>>>(p);
+  sb_launch(attn_prefill_kernel, dim3((unsigned)tiles, n_kv_heads, n_seqs), dim3(128), PREFILL_SMEM,
+            stream, p);
   SB_CHECK_LAUNCH("sb_attention (prefill)");
   return SB_OK;
 }
@@ -559,10 +568,12 @@ extern "C" int sb_attention_decode_static(const void* q, void* out, int n_rows, 
   p.cache = (const bf16*)cache; p.scratch = g_static_scratch_ptr[device];
   p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads; p.window = window; p.n_splits = n_splits;
   p.scale_log2 = scale * LOG2E;
-  attn_decode_kernel<<<dim3(n_splits, n_kv_heads, n_seqs), DEC_WARPS * 32, DECODE_SMEM, stream>>>(p);
+  sb_launch(attn_decode_kernel, dim3(n_splits, n_kv_heads, n_seqs), dim3(DEC_WARPS * 32), DECODE_SMEM,
+            stream, p);
   SB_CHECK_LAUNCH("sb_attention_decode_static (decode)");
   if (n_splits > 1) {
-    attn_merge_kernel<<<dim3(n_rows, n_q_heads), 128, 0, stream>>>(p, nullptr, n_rows);
+    sb_launch(attn_merge_kernel, dim3(n_rows, n_q_heads), dim3(128), 0, stream, p,
+              (const int32_t*)nullptr, n_rows);
     SB_CHECK_LAUNCH("sb_attention_decode_static (merge)");
   }
   return SB_OK;

@@ -29,6 +29,8 @@ attn_plain_kernel(const TQ* __restrict__ q, TQ* __restrict__ out,
   __shared__ float qs[MAX_HD];
   __shared__ float scores[CHUNK];
   __shared__ float bcast[2];
+  sb_pdl_launch();
+  sb_pdl_wait();
   const int t = blockIdx.x, h = blockIdx.y;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int kvh = h / (n_q_heads / n_kv_heads);
@@ -132,7 +134,7 @@ extern "C" int sb_attention_plain(const void* q, void* out, int act_dtype, int n
   const dim3 grid(n_rows, n_q_heads);
   SB_DISPATCH_DTYPE(act_dtype, TQ, {
     SB_DISPATCH_DTYPE(cache_dtype, TC, {
-      attn_plain_kernel<TQ, TC><<<grid, THREADS, 0, stream>>>(
+      sb_launch(attn_plain_kernel<TQ, TC>, grid, dim3(THREADS), 0, stream,
           (const TQ*)q, (TQ*)out, row_seq, row_pos, page_off, page_ids, page_size,
           (const TC*)cache, n_q_heads, n_kv_heads, hd, window, scale);
     });

@@ -66,6 +66,35 @@ __device__ __forceinline__ float sb_warp_max(float v) {
   return v;
 }
 
+// Programmatic dependent launch: every kernel of a step is launched so that it may start
+// while its predecessor in the stream is still running.  A kernel calls sb_pdl_launch() early
+// (its successor may then be scheduled as soon as resources free up) and sb_pdl_wait() before
+// it first touches anything a predecessor wrote; what it does before the wait (barrier set-up,
+// prefetching weights) overlaps the predecessor's tail.  Without the launch attribute both are
+// no-ops.
+__device__ __forceinline__ void sb_pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void sb_pdl_launch() {
+  asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+}
+
+extern "C" int sb_pdl_enabled();      // per library; set with sb_set_pdl
+
+template <typename... Exp, typename... Act>
+inline cudaError_t sb_launch(void (*kernel)(Exp...), dim3 grid, dim3 block, size_t smem,
+                             cudaStream_t stream, Act&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = sb_pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<Exp>(args)...);
+}
+
 // Dispatch helpers: run `BODY` with `T` bound to the C++ type of a dtype code.
 #define SB_DISPATCH_DTYPE(code, T, ...)                           \
   do {                                                            \

@@ -10,6 +10,8 @@ extern "C" int sb_abi_version() { return 1; }
 template <typename TW>
 __global__ void embed_kernel(const int32_t* __restrict__ tokens, const TW* __restrict__ table,
                              int width, float* __restrict__ out) {
+  sb_pdl_launch();
+  sb_pdl_wait();
   const int t = blockIdx.x;
   const TW* row = table + (size_t)tokens[t] * width;
   float* o = out + (size_t)t * width;
@@ -21,7 +23,7 @@ extern "C" int sb_embed(const int32_t* tokens, int n_rows, const void* table, in
   if (n_rows <= 0 || width <= 0) SB_FAIL(SB_ERR_ARG, "sb_embed: n_rows=%d width=%d", n_rows, width);
   if (!sb_valid_dtype(table_dtype)) SB_FAIL(SB_ERR_ARG, "sb_embed: table dtype %d", table_dtype);
   SB_DISPATCH_DTYPE(table_dtype, TW, {
-    embed_kernel<TW><<<n_rows, 256, 0, stream>>>(tokens, (const TW*)table, width, out);
+    sb_launch(embed_kernel<TW>, dim3(n_rows), dim3(256), 0, stream, tokens, (const TW*)table, width, out);
   });
   SB_CHECK_LAUNCH("sb_embed");
   return SB_OK;
@@ -39,6 +41,8 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const int32_t* __res
                                TO* __restrict__ out) {
   __shared__ float warp_sums[32];
   __shared__ float inv_shared;
+  sb_pdl_launch();
+  sb_pdl_wait();
   const int r = blockIdx.x;
   const float* xr = x + (size_t)(rows ? rows[r] : r) * width;
   float s = 0.0f;
@@ -72,8 +76,8 @@ extern "C" int sb_rmsnorm(const float* x, const int32_t* rows, int n_rows, int w
   const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
   SB_DISPATCH_DTYPE(weight_dtype, TW, {
     SB_DISPATCH_DTYPE(out_dtype, TO, {
-      rmsnorm_kernel<TW, TO><<<n_rows, threads, 0, stream>>>(x, rows, (const TW*)weight, width,
-                                                             eps, (TO*)out);
+      sb_launch(rmsnorm_kernel<TW, TO>, dim3(n_rows), dim3(threads), 0, stream, x, rows,
+                (const TW*)weight, width, eps, (TO*)out);
     });
   });
   SB_CHECK_LAUNCH("sb_rmsnorm");
@@ -83,6 +87,8 @@ extern "C" int sb_rmsnorm(const float* x, const int32_t* rows, int n_rows, int w
 // ------------------------------------------------------------------------------------ cast
 template <typename TI, typename TO>
 __global__ void cast_kernel(const TI* __restrict__ in, TO* __restrict__ out, size_t n) {
+  sb_pdl_launch();
+  sb_pdl_wait();
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
        i += (size_t)gridDim.x * blockDim.x)
     out[i] = sb_from_f32<TO>(sb_to_f32<TI>(in[i]));
@@ -96,7 +102,7 @@ extern "C" int sb_cast(const void* in, int in_dtype, void* out, int out_dtype, s
   const int blocks = (int)((n + 255) / 256 < 4096 ? (n + 255) / 256 : 4096);
   SB_DISPATCH_DTYPE(in_dtype, TI, {
     SB_DISPATCH_DTYPE(out_dtype, TO, {
-      cast_kernel<TI, TO><<<blocks, 256, 0, stream>>>((const TI*)in, (TO*)out, n);
+      sb_launch(cast_kernel<TI, TO>, dim3(blocks), dim3(256), 0, stream, (const TI*)in, (TO*)out, n);
     });
   });
   SB_CHECK_LAUNCH("sb_cast");
@@ -122,6 +128,8 @@ __global__ void rope_store_kernel(const float* __restrict__ qkv, int n_q_heads, 
                                   const int32_t* __restrict__ page_off,
                                   const int32_t* __restrict__ page_ids, int page_size,
                                   TC* __restrict__ cache, TQ* __restrict__ q_out, int has_kv) {
+  sb_pdl_launch();
+  sb_pdl_wait();
   const int t = blockIdx.x;
   const int head = blockIdx.y;                       // q heads, then k heads, then v heads
   const int width_in = (n_q_heads + (has_kv ? 2 * n_kv_heads : 0)) * hd;
@@ -170,7 +178,7 @@ extern "C" int sb_rope_store(const float* qkv, int n_rows, int n_q_heads, int n_
   const int threads = hd >= 128 ? 128 : (hd >= 64 ? 64 : 32);
   SB_DISPATCH_DTYPE(q_dtype, TQ, {
     SB_DISPATCH_DTYPE(cache_dtype, TC, {
-      rope_store_kernel<TQ, TC><<<grid, threads, 0, stream>>>(
+      sb_launch(rope_store_kernel<TQ, TC>, grid, dim3(threads), 0, stream,
           qkv, n_q_heads, n_kv_heads, hd, rot, inv_freq, row_seq, row_pos, page_off, page_ids,
           page_size, (TC*)cache, (TQ*)q_out, has_kv);
     });

@@ -1,6 +1,7 @@
 // The last-error string of a kernel library.  Every library built from this folder links its
 // own copy, so a message is read from the library whose call failed.
 #include <stdarg.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 
@@ -15,3 +16,16 @@ void sb_set_error(const char* fmt, ...) {
   va_end(ap);
 }
 
+
+// Whether kernels are launched with programmatic dependent launch (on unless SB_PDL=0).
+static int g_pdl = -1;
+
+extern "C" int sb_pdl_enabled() {
+  if (g_pdl < 0) {
+    const char* e = getenv("SB_PDL");
+    g_pdl = (e && e[0] == '0') ? 0 : 1;
+  }
+  return g_pdl;
+}
+
+extern "C" void sb_set_pdl(int on) { g_pdl = on ? 1 : 0; }

@@ -64,6 +64,7 @@ gemm_skinny_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, int M
                    int epilogue, const void* __restrict__ bias, int bias_dtype,
                    const float* residual, TO* out) {
   __shared__ float partial[SK_WARPS][NT][32][4];
+  sb_pdl_launch();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int m0 = blockIdx.x * 16;
   const uint4* w0 = (const uint4*)(W + (size_t)min(m0 + g, N - 1) * K) + t;
@@ -94,6 +95,8 @@ gemm_skinny_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, int M
       wa[u] = ok[u] ? ldg_stream(w0 + k * 4) : zero;
       wb[u] = ok[u] ? ldg_stream(w1 + k * 4) : zero;
     }
+    // the weights above do not depend on the kernel before this one; everything below does
+    if (kb == warp) sb_pdl_wait();
 #pragma unroll
     for (int u = 0; u < SK_UNROLL; ++u) {
       const int k = kb + u * SK_WARPS;
@@ -105,6 +108,7 @@ gemm_skinny_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, int M
       }
     }
   }
+  if (warp >= n_blocks) sb_pdl_wait();          // a warp without K blocks never waited above
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
@@ -144,7 +148,7 @@ int launch_skinny(const bf16* X, const bf16* W, int M, int N, int K, int epilogu
                   int out_dtype, cudaStream_t stream) {
   const int blocks = (N + 15) / 16;
   SB_DISPATCH_DTYPE(out_dtype, TO, {
-    gemm_skinny_kernel<NT, TO><<<blocks, SK_WARPS * 32, 0, stream>>>(
+    sb_launch(gemm_skinny_kernel<NT, TO>, dim3(blocks), dim3(SK_WARPS * 32), 0, stream,
         X, W, M, N, K, epilogue, bias, bias_dtype, residual, (TO*)out);
   });
   SB_CHECK_LAUNCH("sb_gemm_skinny");
@@ -185,6 +189,8 @@ gemm_tiled_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, int M,
                   const float* residual, TO* out) {
   extern __shared__ __align__(128) unsigned char smem[];
   const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(smem);
+  sb_pdl_launch();
+  sb_pdl_wait();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int warp_m = warp >> 2, warp_n = warp & 3;             // 2 x 4 warps, 64 x 32 each
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
@@ -343,7 +349,7 @@ extern "C" int sb_gemm_tiled(const void* A, int a_dtype, const void* W, int w_dt
         SB_FAIL(SB_ERR_CUDA, "sb_gemm_tiled: shared memory opt-in failed: %s", cudaGetErrorString(e));
       configured[out_dtype] = true;
     }
-    gemm_tiled_kernel<TO><<<grid, TILED_THREADS, TILED_SMEM, stream>>>(
+    sb_launch(gemm_tiled_kernel<TO>, grid, dim3(TILED_THREADS), TILED_SMEM, stream,
         (const bf16*)A, (const bf16*)W, M, N, K, epilogue, bias, bias_dtype, residual, (TO*)out);
   });
   SB_CHECK_LAUNCH("sb_gemm_tiled");

@@ -26,6 +26,8 @@ gemm_plain_kernel(const TA* __restrict__ A, const TW* __restrict__ W, int M, int
   __shared__ float As[TK][TM + 1];
   __shared__ float Ws[TK][TN + 1];
   __shared__ float Cs[TM][TN + 1];
+  sb_pdl_launch();
+  sb_pdl_wait();
   const int tid = threadIdx.x;
   const int tx = tid & 15, ty = tid >> 4;           // 16 x 16 threads, 4 x 4 outputs each
   const int m0 = blockIdx.y * TM, n0 = blockIdx.x * TN;
@@ -124,7 +126,7 @@ extern "C" int sb_gemm_plain(const void* A, int a_dtype, const void* W, int w_dt
   SB_DISPATCH_DTYPE(a_dtype, TA, {
     SB_DISPATCH_DTYPE(w_dtype, TW, {
       SB_DISPATCH_DTYPE(out_dtype, TO, {
-        gemm_plain_kernel<TA, TW, TO><<<grid, 256, 0, stream>>>(
+        sb_launch(gemm_plain_kernel<TA, TW, TO>, grid, dim3(256), 0, stream,
             (const TA*)A, (const TW*)W, M, N, K, epilogue, bias, bias_dtype, residual, (TO*)out);
       });
     });

@@ -172,6 +172,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   __shared__ int s_last;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  sb_pdl_launch();
   // consecutive blocks walk the A tiles of one B tile (or K splits first, in the swapped form),
   // so that a wave of blocks shares its operand tiles through L2
   int tile_a, tile_b, split = 0;
@@ -205,10 +206,26 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   const uint32_t tmem_base = *tmem_slot_ptr;
 
   if (warp == 0 && lane == 0) {
-    // ---- producer
+    // ---- producer.  The weight operand (A when swapped, else B) does not depend on the
+    // kernel before this one, so the first ring of weight tiles is requested before the wait
+    // on that kernel; the activation tiles follow after it.
     int issued = 0;
     bool ok = true;
-    for (int i = 0; i < n_k && ok; ++i) {
+    const int head = min(n_k, STAGES);
+    for (int i = 0; i < head; ++i) {
+      mbar_expect_tx(full0 + 8 * i, stage_bytes(BN));
+      const uint32_t a_dst = tiles + i * stage_bytes(BN), b_dst = a_dst + BM * BK * 2;
+      if (SWAPPED) tma_load_2d(a_dst, &map_a, (k_begin + i) * BK, tile_a * BM, full0 + 8 * i);
+      else         tma_load_2d(b_dst, &map_b, (k_begin + i) * BK, tile_b * BN, full0 + 8 * i);
+    }
+    sb_pdl_wait();
+    for (int i = 0; i < head; ++i) {
+      const uint32_t a_dst = tiles + i * stage_bytes(BN), b_dst = a_dst + BM * BK * 2;
+      if (SWAPPED) tma_load_2d(b_dst, &map_b, (k_begin + i) * BK, tile_b * BN, full0 + 8 * i);
+      else         tma_load_2d(a_dst, &map_a, (k_begin + i) * BK, tile_a * BM, full0 + 8 * i);
+      issued = i + 1;
+    }
+    for (int i = head; i < n_k && ok; ++i) {
       const int s = i % STAGES;
       ok = mbar_wait(empty0 + 8 * s, ((i / STAGES) & 1) ^ 1, 1);
       if (!ok) break;
@@ -243,6 +260,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     umma_commit(acc_bar);                   // arrives when every MMA above has finished
   } else if (warp >= 2) {
     // ---- epilogue: this warp reads TMEM lanes [32 q, 32 q + 32)
+    sb_pdl_wait();                          // the residual, and the scratch of an earlier product
     const int q = warp & 3;
     const bool ok = mbar_wait(acc_bar, 0, 4);
     tc_fence_after();
@@ -328,6 +346,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
 
   if (SWAPPED && p.k_splits > 1) {
+    sb_pdl_wait();
     // The block that arrives last at this tile's counter adds the partial tiles in split order
     // and runs the epilogue; the counter is left at zero for the next launch.
     __threadfence();
@@ -407,7 +426,8 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const Tc5Params& p, int
       SB_FAIL(SB_ERR_CUDA, "sb_gemm_tc5: shared memory opt-in failed: %s", cudaGetErrorString(e));
     configured = true;
   }
-  gemm_tc5_kernel<BN, STAGES, SWAPPED, TO><<<blocks, THREADS, smem, stream>>>(ma, mb, p);
+  sb_launch(gemm_tc5_kernel<BN, STAGES, SWAPPED, TO>, dim3(blocks), dim3(THREADS), smem, stream, ma,
+            mb, p);
   SB_CHECK_LAUNCH("sb_gemm_tc5");
   return SB_OK;
 }

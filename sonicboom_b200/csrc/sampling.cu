@@ -93,6 +93,8 @@ sample_kernel(float* logits, int vocab, const SbSampleParams* __restrict__ param
   __shared__ uint32_t s_prefix, s_need, s_count, s_running;
   __shared__ int s_keep;
 
+  sb_pdl_launch();
+  sb_pdl_wait();
   const int row = blockIdx.x, tid = threadIdx.x;
   SbSampleParams p = params[row];
   // with `fed_pos`, the token produced follows the one fed at fed_pos[row] in this step
@@ -291,6 +293,8 @@ sample_kernel(float* logits, int vocab, const SbSampleParams* __restrict__ param
 }
 
 __global__ void add_kernel(int32_t* x, int n, int delta) {
+  sb_pdl_launch();
+  sb_pdl_wait();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) x[i] += delta;
 }
@@ -300,7 +304,7 @@ __global__ void add_kernel(int32_t* x, int n, int delta) {
 // x[i] += delta: advances the positions of a decode loop that stays on the device.
 extern "C" int sb_add_i32(int32_t* x, int n, int delta, cudaStream_t stream) {
   if (n <= 0) SB_FAIL(SB_ERR_ARG, "sb_add_i32: n=%d", n);
-  add_kernel<<<(n + 255) / 256, 256, 0, stream>>>(x, n, delta);
+  sb_launch(add_kernel, dim3((n + 255) / 256), dim3(256), 0, stream, x, n, delta);
   SB_CHECK_LAUNCH("sb_add_i32");
   return SB_OK;
 }
@@ -319,8 +323,8 @@ extern "C" int sb_sample(float* logits, int n_rows, int vocab, const void* param
   if (history_stride < 0 || history_stride > MAX_HISTORY)
     SB_FAIL(SB_ERR_UNSUPPORTED, "sb_sample: a penalty window of %d tokens is above the cap of %d",
             history_stride, MAX_HISTORY);
-  sample_kernel<<<n_rows, THREADS, 0, stream>>>(logits, vocab, (const SbSampleParams*)params,
-                                                history, history_stride, fed_pos, out_tokens);
+  sb_launch(sample_kernel, dim3(n_rows), dim3(THREADS), 0, stream, logits, vocab,
+            (const SbSampleParams*)params, history, history_stride, fed_pos, out_tokens);
   SB_CHECK_LAUNCH("sb_sample");
   return SB_OK;
 }

@@ -191,6 +191,15 @@ def _tc5_workspace(M: int, N: int, K: int, device):
     return bufs[-1]
 
 
+def set_pdl(on: bool) -> None:
+    """Turns programmatic dependent launch of the kernels on or off (on by default; the
+    environment variable SB_PDL=0 turns it off at start)."""
+    lib().sb_set_pdl(1 if on else 0)
+    for l in _attn_libs.values():
+        if l is not None:
+            l.sb_set_pdl(1 if on else 0)
+
+
 def tc5_status() -> int:
     """0 unless a tcgen05 kernel gave up on a bounded wait since the last call (synchronizes)."""
     return int(lib().sb_tc5_status())
