@@ -12,12 +12,12 @@
 //
 //  * prefill kernel: 64 rows per block (4 warps x 16), key tiles of one cache page (64 keys)
 //    taken in ascending order with a double-buffered cp.async pipeline, online softmax.
-//  * decode kernel (at most 16 rows per sequence and head): the keys are cut into splits of 128
-//    at absolute positions; a block takes one split, each of its 2 warps one page of it (small
-//    blocks, so that three of them fit an SM and their loads overlap each other's math); the
-//    warps' partial (m, l, o) are merged in warp order, and when a sequence has more than one
-//    split the blocks' partials go to scratch memory and a second kernel merges them in
-//    ascending order (core/src/model/emit.cpp:538-560 "chunk_index_asc",
+//  * decode kernel (at most 16 rows per sequence and head): the keys are cut into splits of 256
+//    at absolute positions; a block streams one split through double-buffered 64-key tiles,
+//    each of its 4 warps taking 16 keys of every tile; the warps' partial (m, l, o) are merged
+//    in warp order.  When a sequence has more than one split the blocks' partials go to scratch
+//    memory, and the block that finishes last for a (sequence, key/value head) merges them in
+//    ascending split order (core/src/model/emit.cpp:538-560 "chunk_index_asc",
 //    core/src/nn/cuda_elementwise.cu:852-1017).  Tile and split boundaries depend only on
 //    key positions, so a result does not depend on the batch or on where the pages lie.
 //
@@ -39,8 +39,8 @@ constexpr int HD = SB_HD;
 constexpr int KT = 64;                 // keys per tile = cache page size
 constexpr int LDS = HD + 8;            // shared-memory row stride: an odd number of 16-byte chunks
 constexpr int BM = 64;                 // prefill rows per block
-constexpr int DEC_WARPS = 2;           // decode: warps per block, one cache page each
-constexpr int SPLIT_PAGES = DEC_WARPS; // decode: pages per split (128 keys)
+constexpr int DEC_WARPS = 4;           // decode: warps per block, 16 keys of every tile each
+constexpr int SPLIT_PAGES = 4;         // decode: pages per split (256 keys)
 constexpr int DEC_ROWS = 16;
 constexpr float LOG2E = 1.4426950408889634f;
 
@@ -55,6 +55,7 @@ struct AttnParams {
   const int32_t* page_ids;
   const bf16* cache;           // [page][k|v][kv head][KT][HD]
   float* scratch;
+  int* counters;               // one per (sequence, key/value head), zero between launches
   int n_q_heads, n_kv_heads, window, n_splits;
   float scale_log2;            // scale * log2(e)
 };
@@ -108,19 +109,20 @@ __device__ __forceinline__ void load_kv_tile(uint32_t ks, uint32_t vs, const bf1
 
 // One key tile for a warp's 16 rows: scores, mask, online softmax update, P.V.
 // `pos_a`, `pos_b`: positions of the thread's two rows (g and g + 8), -1 for padding rows.
+template <int NKEYS>
 __device__ __forceinline__ void tile_step(const uint32_t (&qf)[HD / 16][4], uint32_t ks,
                                           uint32_t vs, int key0, int pos_a, int pos_b, int window,
                                           float scale_log2, float (&m)[2], float (&l)[2],
                                           float (&o)[HD / 8][4], int lane) {
-  float s[KT / 8][4];
+  float s[NKEYS / 8][4];
 #pragma unroll
-  for (int j = 0; j < KT / 8; ++j)
+  for (int j = 0; j < NKEYS / 8; ++j)
 #pragma unroll
     for (int i = 0; i < 4; ++i) s[j][i] = 0.0f;
 #pragma unroll
   for (int kk = 0; kk < HD / 16; ++kk) {
 #pragma unroll
-    for (int j = 0; j < KT / 16; ++j) {
+    for (int j = 0; j < NKEYS / 16; ++j) {
       const int row = j * 16 + (lane & 7) + ((lane >> 4) << 3);
       const int col = kk * 16 + ((lane >> 3) & 1) * 8;
       uint32_t b0, b1, b2, b3;
@@ -132,7 +134,7 @@ __device__ __forceinline__ void tile_step(const uint32_t (&qf)[HD / 16][4], uint
   const int t = lane & 3;
   float tmax[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-  for (int j = 0; j < KT / 8; ++j) {
+  for (int j = 0; j < NKEYS / 8; ++j) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int key = key0 + j * 8 + 2 * t + (i & 1);
@@ -160,7 +162,7 @@ __device__ __forceinline__ void tile_step(const uint32_t (&qf)[HD / 16][4], uint
     o[j][2] *= alpha[1]; o[j][3] *= alpha[1];
   }
 #pragma unroll
-  for (int j = 0; j < KT / 8; ++j) {
+  for (int j = 0; j < NKEYS / 8; ++j) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const float p = exp2f(s[j][i] - base[i >> 1]);
@@ -169,7 +171,7 @@ __device__ __forceinline__ void tile_step(const uint32_t (&qf)[HD / 16][4], uint
     }
   }
 #pragma unroll
-  for (int kk = 0; kk < KT / 16; ++kk) {
+  for (int kk = 0; kk < NKEYS / 16; ++kk) {
     uint32_t a[4];
     a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
     a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
@@ -252,7 +254,7 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const AttnParams p) {
       cp_async_wait<0>();
     }
     __syncthreads();
-    tile_step(qf, ks, vs, tile * KT, pos_a, pos_b, p.window, p.scale_log2, m, l, o, lane);
+    tile_step<KT>(qf, ks, vs, tile * KT, pos_a, pos_b, p.window, p.scale_log2, m, l, o, lane);
     __syncthreads();
   }
 
@@ -276,17 +278,19 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const AttnParams p) {
 }
 
 // -------------------------------------------------------------------------------- decode
-// Shared memory: Q [16][LDS] bf16, then per warp K and V tiles [64][LDS]; after the keys are
-// done the tiles' space is reused for the warps' partial outputs.
-constexpr int DECODE_SMEM = (DEC_ROWS + DEC_WARPS * 2 * KT) * LDS * 2;
+// Shared memory: Q [16][LDS] bf16, then two stages of K and V tiles [64][LDS]; after the keys
+// are done the tiles' space is reused for the warps' partial outputs.
+constexpr int DECODE_SMEM = (DEC_ROWS + 4 * KT) * LDS * 2;
 constexpr int PART_STRIDE = HD + 2;    // floats per partial row: o[HD], m, l
-// The largest head sizes do not leave room for the warps' tiles in one block's shared memory
-// (227 KiB); their decode steps run through the prefill kernel instead.
 constexpr bool DECODE_FITS = DECODE_SMEM <= 227 * 1024;
+static_assert(DEC_WARPS * 16 == KT, "each warp takes 16 keys of a tile");
+static_assert(DEC_WARPS * DEC_ROWS * PART_STRIDE * 4 <= 4 * KT * LDS * 2, "partials fit the tiles");
 
 __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(const AttnParams p) {
   extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ int s_last;
   const uint32_t qs = (uint32_t)__cvta_generic_to_shared(smem);
+  const uint32_t kv0 = qs + DEC_ROWS * LDS * 2;               // K0, V0, K1, V1
   sb_pdl_launch();
   sb_pdl_wait();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -299,8 +303,8 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(const AttnP
   const int split_lo = key_lo / (SPLIT_PAGES * KT), split_hi = p_hi / (SPLIT_PAGES * KT);
   if (split < split_lo || split > split_hi) return;
   const int32_t* pages = p.page_ids + p.page_off[b];
-  const int tile = split * SPLIT_PAGES + warp;
-  const bool has_tile = tile >= key_lo / KT && tile <= p_hi / KT;
+  const int tile_lo = max(split * SPLIT_PAGES, key_lo / KT);
+  const int tile_hi = min(split * SPLIT_PAGES + SPLIT_PAGES - 1, p_hi / KT);
 
   for (int idx = tid; idx < DEC_ROWS * (HD / 8); idx += DEC_WARPS * 32) {
     const int row = idx / (HD / 8), ch = idx % (HD / 8);
@@ -309,11 +313,8 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(const AttnP
     cp_async16(qs + (uint32_t)(row * LDS + ch * 8) * 2,
                p.q + ((size_t)(row0 + t) * p.n_q_heads + kvh * G + g) * HD + ch * 8, valid);
   }
-  const uint32_t ks = qs + (DEC_ROWS + warp * 2 * KT) * LDS * 2, vs = ks + KT * LDS * 2;
-  if (has_tile) load_kv_tile(ks, vs, p.cache, pages[tile], p.n_kv_heads, kvh, lane, 32);
+  load_kv_tile(kv0, kv0 + KT * LDS * 2, p.cache, pages[tile_lo], p.n_kv_heads, kvh, tid, DEC_WARPS * 32);
   cp_async_commit();
-  cp_async_wait<0>();
-  __syncthreads();
 
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
   float o[HD / 8][4];
@@ -322,18 +323,33 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(const AttnP
 #pragma unroll
     for (int i = 0; i < 4; ++i) o[j][i] = 0.0f;
   const int ra = lane >> 2, rb = ra + 8;
-  if (has_tile) {
-    uint32_t qf[HD / 16][4];
-    load_q_frags(qs, 0, lane, qf);
-    const int pos_a = ra < R ? pos0 + ra / G : -1, pos_b = rb < R ? pos0 + rb / G : -1;
-    tile_step(qf, ks, vs, tile * KT, pos_a, pos_b, p.window, p.scale_log2, m, l, o, lane);
+  const int pos_a = ra < R ? pos0 + ra / G : -1, pos_b = rb < R ? pos0 + rb / G : -1;
+  uint32_t qf[HD / 16][4];
+
+  for (int tile = tile_lo; tile <= tile_hi; ++tile) {
+    const int stage = (tile - tile_lo) & 1;
+    const uint32_t ks = kv0 + stage * 2 * KT * LDS * 2, vs = ks + KT * LDS * 2;
+    if (tile < tile_hi) {
+      const uint32_t nk = kv0 + (stage ^ 1) * 2 * KT * LDS * 2;
+      load_kv_tile(nk, nk + KT * LDS * 2, p.cache, pages[tile + 1], p.n_kv_heads, kvh, tid, DEC_WARPS * 32);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    if (tile == tile_lo) load_q_frags(qs, 0, lane, qf);
+    // this warp's 16 keys of the tile
+    const uint32_t off = (uint32_t)(warp * 16 * LDS) * 2;
+    tile_step<16>(qf, ks + off, vs + off, tile * KT + warp * 16, pos_a, pos_b, p.window, p.scale_log2,
+                  m, l, o, lane);
+    __syncthreads();
   }
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
     l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
     l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
   }
-  __syncthreads();                                   // every warp is done with its tiles
   float* part = reinterpret_cast<float*>(smem + DEC_ROWS * LDS * 2);   // [warp][16][PART_STRIDE]
   const int t4 = lane & 3;
 #pragma unroll
@@ -350,13 +366,14 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(const AttnP
     }
   }
   __syncthreads();
-  // merge the warps in warp order: thread handles (row, d) pairs
+  // merge the warps in warp order: a thread handles (row, d) pairs
   const bool single = split_lo == split_hi;
   for (int idx = tid; idx < R * HD; idx += DEC_WARPS * 32) {
     const int row = idx / HD, d = idx % HD;
     float mm = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < DEC_WARPS; ++w) mm = fmaxf(mm, part[((size_t)w * DEC_ROWS + row) * PART_STRIDE + HD]);
+    for (int w = 0; w < DEC_WARPS; ++w)
+      mm = fmaxf(mm, part[((size_t)w * DEC_ROWS + row) * PART_STRIDE + HD]);
     const float base = mm == -INFINITY ? 0.0f : mm;
     float acc = 0.0f, ll = 0.0f;
 #pragma unroll
@@ -380,40 +397,37 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(const AttnP
       }
     }
   }
-}
+  if (single) return;
 
-// Merges a row's splits in ascending order.  Grid: (rows, query heads).
-__global__ void __launch_bounds__(128)
-attn_merge_kernel(const AttnParams p, const int32_t* __restrict__ row_seq_unused, int n_rows) {
-  const int row = blockIdx.x, head = blockIdx.y;
-  // find the sequence of this row by its row range (few sequences; linear scan by one thread)
-  __shared__ int s_lo, s_hi;
-  sb_pdl_launch();
-  sb_pdl_wait();
-  if (threadIdx.x == 0) {
-    int b = 0;
-    while (p.seq_row0[b + 1] <= row) ++b;
-    const int pos0 = p.seq_pos0[b], n_new = p.seq_row0[b + 1] - p.seq_row0[b];
-    const int key_lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
-    s_lo = key_lo / (SPLIT_PAGES * KT);
-    s_hi = (pos0 + n_new - 1) / (SPLIT_PAGES * KT);
+  // The block that finishes last for this (sequence, key/value head) merges its splits in
+  // ascending order; the counter is left at zero for the next launch.
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    int* counter = p.counters + (size_t)b * p.n_kv_heads + kvh;
+    const int seen = atomicAdd(counter, 1);
+    s_last = seen == split_hi - split_lo;
+    if (s_last) *counter = 0;
   }
   __syncthreads();
-  const int lo = s_lo, hi = s_hi;
-  if (lo == hi) return;                              // the decode kernel wrote the output itself
-  const float* base = p.scratch + ((size_t)row * p.n_q_heads + head) * p.n_splits * PART_STRIDE;
-  float mm = -INFINITY;
-  for (int s = lo; s <= hi; ++s) mm = fmaxf(mm, base[(size_t)s * PART_STRIDE + HD]);
-  const float ref = mm == -INFINITY ? 0.0f : mm;
-  for (int d = threadIdx.x; d < HD; d += 128) {
+  if (!s_last) return;
+  __threadfence();
+  for (int idx = tid; idx < R * HD; idx += DEC_WARPS * 32) {
+    const int row = idx / HD, d = idx % HD;
+    const int tok = row / G, g = row % G;
+    const size_t out_row = (size_t)(row0 + tok) * p.n_q_heads + kvh * G + g;
+    const float* base = p.scratch + out_row * p.n_splits * PART_STRIDE;
+    float mm = -INFINITY;
+    for (int s = split_lo; s <= split_hi; ++s) mm = fmaxf(mm, base[(size_t)s * PART_STRIDE + HD]);
+    const float ref = mm == -INFINITY ? 0.0f : mm;
     float acc = 0.0f, ll = 0.0f;
-    for (int s = lo; s <= hi; ++s) {
+    for (int s = split_lo; s <= split_hi; ++s) {
       const float* src = base + (size_t)s * PART_STRIDE;
       const float f = exp2f(src[HD] - ref);
       acc += src[d] * f;
       ll += src[HD + 1] * f;
     }
-    p.out[((size_t)row * p.n_q_heads + head) * HD + d] = __float2bfloat16_rn(acc / ll);
+    p.out[out_row * HD + d] = __float2bfloat16_rn(acc / ll);
   }
 }
 
@@ -436,12 +450,14 @@ extern "C" size_t sb_attention_scratch_bytes(int n_rows, int n_q_heads, int n_kv
 // q [rows, heads, HD] and out [rows, heads*HD] bfloat16; cache: one schedule entry's pages,
 // bfloat16; max_new / max_len: upper bounds of new rows per sequence and of any sequence's
 // length after this step (they size the grid; the true values are read on the device).
+// counters: n_counters ints that are zero (the kernel leaves them zero), at least sequences x
+// key/value heads of them when scratch is needed.
 extern "C" int sb_attention(const void* q, void* out, int n_rows, int n_seqs, int max_new,
                             const int32_t* seq_row0, const int32_t* seq_pos0,
                             const int32_t* page_off, const int32_t* page_ids, int page_size,
                             const void* cache, int n_q_heads, int n_kv_heads, int hd, int window,
-                            float scale, void* scratch, size_t scratch_bytes, int max_len,
-                            cudaStream_t stream) {
+                            float scale, void* scratch, size_t scratch_bytes, int* counters,
+                            int n_counters, int max_len, cudaStream_t stream) {
   if (hd != HD) SB_FAIL(SB_ERR_ARG, "sb_attention: built for head size %d, called with %d", HD, hd);
   if (page_size != KT)
     SB_FAIL(SB_ERR_UNSUPPORTED, "sb_attention: cache pages of %d keys (needs %d)", page_size, KT);
@@ -457,7 +473,7 @@ extern "C" int sb_attention(const void* q, void* out, int n_rows, int n_seqs, in
   AttnParams p;
   p.q = (const bf16*)q; p.out = (bf16*)out;
   p.seq_row0 = seq_row0; p.seq_pos0 = seq_pos0; p.page_off = page_off; p.page_ids = page_ids;
-  p.cache = (const bf16*)cache; p.scratch = (float*)scratch;
+  p.cache = (const bf16*)cache; p.scratch = (float*)scratch; p.counters = counters;
   p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads; p.window = window;
   p.scale_log2 = scale * LOG2E;
   const int G = n_q_heads / n_kv_heads;
@@ -478,15 +494,12 @@ extern "C" int sb_attention(const void* q, void* out, int n_rows, int n_seqs, in
     const size_t need = sb_attention_scratch_bytes(n_rows, n_q_heads, n_kv_heads, max_new, max_len);
     if (need > scratch_bytes || (need && !scratch))
       SB_FAIL(SB_ERR_ARG, "sb_attention: %zu bytes of scratch needed, %zu given", need, scratch_bytes);
+    if (need && (!counters || n_counters < n_seqs * n_kv_heads))
+      SB_FAIL(SB_ERR_ARG, "sb_attention: %d zeroed counters needed, %d given", n_seqs * n_kv_heads,
+              n_counters);
     sb_launch(attn_decode_kernel, dim3(p.n_splits, n_kv_heads, n_seqs), dim3(DEC_WARPS * 32),
               DECODE_SMEM, stream, p);
     SB_CHECK_LAUNCH("sb_attention (decode)");
-    if (p.n_splits > 1) {
-      if (n_q_heads > 65535) SB_FAIL(SB_ERR_UNSUPPORTED, "sb_attention: %d heads", n_q_heads);
-      sb_launch(attn_merge_kernel, dim3(n_rows, n_q_heads), dim3(128), 0, stream, p,
-                (const int32_t*)nullptr, n_rows);
-      SB_CHECK_LAUNCH("sb_attention (merge)");
-    }
     return SB_OK;
   }
   p.n_splits = 1;
@@ -507,9 +520,14 @@ namespace {
 // In host code this name is only a handle for the runtime; it is not a device address.  The
 // address the kernels get comes from cudaGetSymbolAddress below.
 static __device__ __align__(256) unsigned char g_static_scratch[SB_STATIC_SCRATCH_BYTES];
+// Arrival counters of the split merge, one per (sequence, key/value head); zero at load and
+// left at zero by every launch.
+constexpr int STATIC_COUNTERS = 16384;
+static __device__ int g_static_counters[STATIC_COUNTERS];
 
 constexpr int MAX_DEVICES = 64;
 float* g_static_scratch_ptr[MAX_DEVICES] = {};     // per device, filled at that device's first call
+int* g_static_counters_ptr[MAX_DEVICES] = {};
 
 }  // namespace
 
@@ -539,6 +557,9 @@ extern "C" int sb_attention_decode_static(const void* q, void* out, int n_rows, 
             "head size is too large for the decode kernel)", who, max_new, G, DEC_ROWS);
   const int n_splits = n_splits_for(max_len);
   const size_t need = (size_t)n_rows * n_q_heads * n_splits * PART_STRIDE * sizeof(float);
+  if ((long)n_seqs * n_kv_heads > STATIC_COUNTERS)
+    SB_FAIL(SB_ERR_UNSUPPORTED, "%s: %d sequences x %d key/value heads is above the %d built-in "
+            "merge counters", who, n_seqs, n_kv_heads, STATIC_COUNTERS);
   if (need > SB_STATIC_SCRATCH_BYTES)
     SB_FAIL(SB_ERR_UNSUPPORTED,
             "%s: this step needs %zu bytes of scratch, the built-in array holds %u "
@@ -559,6 +580,11 @@ extern "C" int sb_attention_decode_static(const void* q, void* out, int n_rows, 
                              DECODE_SMEM);
     if (e != cudaSuccess)
       SB_FAIL(SB_ERR_CUDA, "%s: shared memory opt-in failed: %s", who, cudaGetErrorString(e));
+    void* cptr = nullptr;
+    e = cudaGetSymbolAddress(&cptr, g_static_counters);
+    if (e != cudaSuccess || !cptr)
+      SB_FAIL(SB_ERR_CUDA, "%s: cudaGetSymbolAddress: %s", who, cudaGetErrorString(e));
+    g_static_counters_ptr[device] = (int*)cptr;
     g_static_scratch_ptr[device] = (float*)ptr;
   }
 
@@ -566,15 +592,11 @@ extern "C" int sb_attention_decode_static(const void* q, void* out, int n_rows, 
   p.q = (const bf16*)q; p.out = (bf16*)out;
   p.seq_row0 = seq_row0; p.seq_pos0 = seq_pos0; p.page_off = page_off; p.page_ids = page_ids;
   p.cache = (const bf16*)cache; p.scratch = g_static_scratch_ptr[device];
+  p.counters = g_static_counters_ptr[device];
   p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads; p.window = window; p.n_splits = n_splits;
   p.scale_log2 = scale * LOG2E;
   sb_launch(attn_decode_kernel, dim3(n_splits, n_kv_heads, n_seqs), dim3(DEC_WARPS * 32), DECODE_SMEM,
             stream, p);
   SB_CHECK_LAUNCH("sb_attention_decode_static (decode)");
-  if (n_splits > 1) {
-    sb_launch(attn_merge_kernel, dim3(n_rows, n_q_heads), dim3(128), 0, stream, p,
-              (const int32_t*)nullptr, n_rows);
-    SB_CHECK_LAUNCH("sb_attention_decode_static (merge)");
-  }
   return SB_OK;
 }

@@ -21,10 +21,9 @@ constexpr int MAX_HD = 256;
 
 template <typename TQ, typename TC>
 __global__ void __launch_bounds__(THREADS)
-attn_plain_kernel(const TQ* __restrict__ q, TQ* __restrict__ out,
-                  const int32_t* __restrict__ row_seq, const int32_t* __restrict__ row_pos,
-                  const int32_t* __restrict__ page_off, const int32_t* __restrict__ page_ids,
-                  int page_size, const TC* __restrict__ cache, int n_q_heads, int n_kv_heads,
+attn_plain_kernel(const TQ* q, TQ* out, const int32_t* row_seq, const int32_t* row_pos,
+                  const int32_t* page_off, const int32_t* page_ids, int page_size,
+                  const TC* cache, int n_q_heads, int n_kv_heads,
                   int hd, int window, float scale) {
   __shared__ float qs[MAX_HD];
   __shared__ float scores[CHUNK];

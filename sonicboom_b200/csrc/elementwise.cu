@@ -7,8 +7,11 @@ extern "C" int sb_abi_version() { return 1; }
 // ------------------------------------------------------------------------------- embedding
 // x[t, :] = E[tokens[t], :] as float32; no sqrt(width) scale for this architecture
 // (core/src/model/emit.cpp:237-247, core/src/nn/embedding.cpp:23-28).
+// Inputs that an earlier kernel of the step wrote are plain pointers, not `const __restrict__`:
+// with programmatic dependent launch a kernel may start before its predecessor has finished, and
+// the non-coherent load path that `const __restrict__` selects could then return stale lines.
 template <typename TW>
-__global__ void embed_kernel(const int32_t* __restrict__ tokens, const TW* __restrict__ table,
+__global__ void embed_kernel(const int32_t* tokens, const TW* __restrict__ table,
                              int width, float* __restrict__ out) {
   sb_pdl_launch();
   sb_pdl_wait();
@@ -36,7 +39,7 @@ extern "C" int sb_embed(const int32_t* tokens, int n_rows, const void* table, in
 // order), so a row's result does not depend on which other rows are in the launch.
 // `rows`, when given, gathers: output row r is the norm of input row rows[r].
 template <typename TW, typename TO>
-__global__ void rmsnorm_kernel(const float* __restrict__ x, const int32_t* __restrict__ rows,
+__global__ void rmsnorm_kernel(const float* x, const int32_t* rows,
                                const TW* __restrict__ w, int width, float eps,
                                TO* __restrict__ out) {
   __shared__ float warp_sums[32];
@@ -86,7 +89,7 @@ extern "C" int sb_rmsnorm(const float* x, const int32_t* rows, int n_rows, int w
 
 // ------------------------------------------------------------------------------------ cast
 template <typename TI, typename TO>
-__global__ void cast_kernel(const TI* __restrict__ in, TO* __restrict__ out, size_t n) {
+__global__ void cast_kernel(const TI* in, TO* out, size_t n) {
   sb_pdl_launch();
   sb_pdl_wait();
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
@@ -121,13 +124,11 @@ extern "C" int sb_cast(const void* in, int in_dtype, void* out, int out_dtype, s
 // Cache of one schedule entry: [page][k|v][kv head][slot in page][hd].  The page of position p
 // of sequence b is page_ids[page_off[b] + p / page_size].
 template <typename TQ, typename TC>
-__global__ void rope_store_kernel(const float* __restrict__ qkv, int n_q_heads, int n_kv_heads,
+__global__ void rope_store_kernel(const float* qkv, int n_q_heads, int n_kv_heads,
                                   int hd, int rot, const float* __restrict__ inv_freq,
-                                  const int32_t* __restrict__ row_seq,
-                                  const int32_t* __restrict__ row_pos,
-                                  const int32_t* __restrict__ page_off,
-                                  const int32_t* __restrict__ page_ids, int page_size,
-                                  TC* __restrict__ cache, TQ* __restrict__ q_out, int has_kv) {
+                                  const int32_t* row_seq, const int32_t* row_pos,
+                                  const int32_t* page_off, const int32_t* page_ids,
+                                  int page_size, TC* cache, TQ* q_out, int has_kv) {
   sb_pdl_launch();
   sb_pdl_wait();
   const int t = blockIdx.x;

@@ -36,9 +36,10 @@ __device__ __forceinline__ uint4 ldg_stream(const uint4* p) {
   return v;
 }
 
+// Activations come from the kernel before this one: a coherent load, never the .nc path.
 __device__ __forceinline__ uint4 ldg_cached(const uint4* p) {
   uint4 v;
-  asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+  asm volatile("ld.global.v4.u32 {%0,%1,%2,%3}, [%4];\n"
                : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
                : "l"(p));
   return v;
@@ -60,7 +61,7 @@ constexpr int SK_UNROLL = 4;     // 32-wide K blocks a warp has in flight
 // assignment is as good as the canonical interleaved one.
 template <int NT, typename TO>
 __global__ void __launch_bounds__(SK_WARPS * 32)
-gemm_skinny_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, int M, int N, int K,
+gemm_skinny_kernel(const bf16* X, const bf16* __restrict__ W, int M, int N, int K,
                    int epilogue, const void* __restrict__ bias, int bias_dtype,
                    const float* residual, TO* out) {
   __shared__ float partial[SK_WARPS][NT][32][4];
@@ -184,7 +185,7 @@ __device__ __forceinline__ uint32_t tile_offset(int row, int chunk) {
 
 template <typename TO>
 __global__ void __launch_bounds__(TILED_THREADS)
-gemm_tiled_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, int M, int N, int K,
+gemm_tiled_kernel(const bf16* A, const bf16* __restrict__ W, int M, int N, int K,
                   int epilogue, const void* __restrict__ bias, int bias_dtype,
                   const float* residual, TO* out) {
   extern __shared__ __align__(128) unsigned char smem[];

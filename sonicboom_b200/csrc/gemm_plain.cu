@@ -20,7 +20,7 @@ constexpr int TM = 64, TN = 64, TK = 16;
 
 template <typename TA, typename TW, typename TO>
 __global__ void __launch_bounds__(256)
-gemm_plain_kernel(const TA* __restrict__ A, const TW* __restrict__ W, int M, int N, int K,
+gemm_plain_kernel(const TA* A, const TW* __restrict__ W, int M, int N, int K,
                   int epilogue, const void* __restrict__ bias, int bias_dtype,
                   const float* residual, TO* out) {
   __shared__ float As[TK][TM + 1];

@@ -6,7 +6,7 @@
 // real-time loop, a callback of another framework that owns the allocator, a process whose
 // memory budget was handed out in full at start-up).  The ordinary entry point, sb_attention,
 // asks its caller for scratch memory whenever a sequence is long enough to be cut into more
-// than one split of 128 keys; such a caller has nowhere to get it from.
+// than one split of 256 keys; such a caller has nowhere to get it from.
 //
 // Here the scratch is a fixed array inside the library's own device image
 // (SB_STATIC_SCRATCH_BYTES, 8 MiB per GPU that loads the library, held until the process
@@ -16,11 +16,12 @@
 // Limits and rules:
 //  * Decode steps only: new rows per sequence x (query heads / key-value heads) <= 16.
 //  * The step must need at most SB_STATIC_SCRATCH_BYTES of scratch, i.e.
-//    rows x query heads x ceil(max_len / 128) x (head size + 2) x 4 bytes; larger steps are
+//    rows x query heads x ceil(max_len / 256) x (head size + 2) x 4 bytes; larger steps are
 //    refused with SB_ERR_UNSUPPORTED and a message that states both numbers.
 //  * The first call on a device looks the array's device address up (cudaGetSymbolAddress,
 //    with that device current) and remembers it; make that first call outside any stream
 //    capture.
+//  * At most 16384 (sequence, key/value head) pairs per step (the built-in merge counters).
 //  * All calls on a device share the one array.  It keeps whatever the last call left in it;
 //    this kernel writes every partial result before it reads it, so nothing needs clearing.
 //    Two calls whose kernels overlap on the GPU (different streams, no ordering between them)

@@ -81,9 +81,8 @@ __device__ int block_argmax(float v, int id, float* sv, int* si) {
 }
 
 __global__ void __launch_bounds__(THREADS)
-sample_kernel(float* logits, int vocab, const SbSampleParams* __restrict__ params,
-              const int32_t* __restrict__ history, int history_stride,
-              const int32_t* __restrict__ fed_pos, int32_t* __restrict__ out_tokens) {
+sample_kernel(float* logits, int vocab, const SbSampleParams* params, const int32_t* history,
+              int history_stride, const int32_t* fed_pos, int32_t* out_tokens) {
   __shared__ int32_t h_tok[MAX_HISTORY];
   __shared__ float h_old[MAX_HISTORY];
   __shared__ uint32_t hist[256];

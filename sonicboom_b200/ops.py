@@ -226,6 +226,17 @@ def rope_store(qkv: torch.Tensor, n_q_heads: int, n_kv_heads: int, head_dim: int
 
 
 _attn_libs: dict = {}
+_attn_counter_bufs: dict = {}    # device -> zeroed int32 buffers (kernels leave them zero; never freed)
+
+
+def _attn_counters(n: int, device) -> torch.Tensor:
+    """Arrival counters of the split attention's merge: zero between launches."""
+    key = torch.device(device).index or 0
+    bufs = _attn_counter_bufs.setdefault(key, [])
+    if not bufs or bufs[-1].numel() < n:
+        bufs.append(torch.zeros(max(n, 1 << 16), dtype=torch.int32, device=device))
+    return bufs[-1]
+
 
 
 def attention_lib(head_dim: int):
@@ -256,16 +267,18 @@ def attention(q: torch.Tensor, out: torch.Tensor, plan, group_index: int, cache:
     if al is not None:
         need = int(al.sb_attention_scratch_bytes(n, n_q_heads, n_kv_heads, plan.max_new, plan.max_len))
         scratch = plan.scratch(need, q.device)
+        counters = _attn_counters(plan.n_seqs * n_kv_heads, q.device)
         rc = al.sb_attention(
             _ptr(q), _ptr(out), n, plan.n_seqs, plan.max_new, _i32(plan.seq_row0, "seq_row0"),
             _i32(plan.seq_pos0, "seq_pos0"), _i32(g.page_off, "page_off"),
             _i32(g.page_ids, "page_ids"), g.page_size, _ptr(cache), n_q_heads, n_kv_heads,
             head_dim, window, ctypes.c_float(scale), _ptr(scratch),
-            ctypes.c_size_t(scratch.numel() if scratch is not None else 0), plan.max_len, _stream())
+            ctypes.c_size_t(scratch.numel() if scratch is not None else 0),
+            _ptr(counters), counters.numel(), plan.max_len, _stream())
         if rc != 0:
             raise KernelError(f"attention: {al.sb_last_error().decode()}")
         global LAUNCHES
-        LAUNCHES += 2 if need else 1
+        LAUNCHES += 1
     else:
         _check(lib().sb_attention_plain(
             _ptr(q), _ptr(out), _code(q.dtype), n, _i32(plan.row_seq, "row_seq"),
