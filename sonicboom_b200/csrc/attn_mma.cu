@@ -10,7 +10,7 @@
 // decode alike (the reference's tensor-core kernels pack the group the same way,
 // core/src/nn/boom_fdec_device.cuh:17-30, core/src/nn/boom_fattn.cu:37-84).
 //
-//  * prefill kernel: 64 rows per block (4 warps x 16), key tiles of one cache page (64 keys)
+//  * prefill kernel: 128 rows per block (8 warps x 16; 64 rows above head size 128), key tiles of one cache page (64 keys)
 //    taken in ascending order with a double-buffered cp.async pipeline, online softmax.
 //  * decode kernel (at most 16 rows per sequence and head): the keys are cut into splits of 256
 //    at absolute positions; a block streams one split through double-buffered 64-key tiles,
@@ -38,7 +38,8 @@ typedef __nv_bfloat16 bf16;
 constexpr int HD = SB_HD;
 constexpr int KT = 64;                 // keys per tile = cache page size
 constexpr int LDS = HD + 8;            // shared-memory row stride: an odd number of 16-byte chunks
-constexpr int BM = 64;                 // prefill rows per block
+constexpr int BM = HD <= 128 ? 128 : 64;  // prefill rows per block (16 per warp); registers bound it
+constexpr int PREFILL_THREADS = BM / 16 * 32;
 constexpr int DEC_WARPS = 4;           // decode: warps per block, 16 keys of every tile each
 constexpr int SPLIT_PAGES = 4;         // decode: pages per split (256 keys)
 constexpr int DEC_ROWS = 16;
@@ -201,7 +202,7 @@ __device__ __forceinline__ void load_q_frags(uint32_t qs, int warp_row0, int lan
 // ------------------------------------------------------------------------------- prefill
 constexpr int PREFILL_SMEM = (BM + 4 * KT) * LDS * 2;
 
-__global__ void __launch_bounds__(128) attn_prefill_kernel(const AttnParams p) {
+__global__ void __launch_bounds__(PREFILL_THREADS) attn_prefill_kernel(const AttnParams p) {
   extern __shared__ __align__(128) unsigned char smem[];
   const uint32_t qs = (uint32_t)__cvta_generic_to_shared(smem);
   const uint32_t kv0 = qs + BM * LDS * 2;                     // K0, V0, K1, V1
@@ -215,7 +216,7 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const AttnParams p) {
   if (r_base >= R) return;
   const int32_t* pages = p.page_ids + p.page_off[b];
 
-  for (int idx = tid; idx < BM * (HD / 8); idx += 128) {
+  for (int idx = tid; idx < BM * (HD / 8); idx += PREFILL_THREADS) {
     const int row = idx / (HD / 8), ch = idx % (HD / 8);
     const int r = r_base + row;
     const bool valid = r < R;
@@ -226,7 +227,7 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const AttnParams p) {
   const int r_last = min(R, r_base + BM) - 1;
   const int p_lo = pos0 + r_base / G, p_hi = pos0 + r_last / G;
   const int tile_lo = (p.window > 0 ? max(0, p_lo - p.window + 1) : 0) / KT, tile_hi = p_hi / KT;
-  load_kv_tile(kv0, kv0 + KT * LDS * 2, p.cache, pages[tile_lo], p.n_kv_heads, kvh, tid, 128);
+  load_kv_tile(kv0, kv0 + KT * LDS * 2, p.cache, pages[tile_lo], p.n_kv_heads, kvh, tid, PREFILL_THREADS);
   cp_async_commit();
   cp_async_wait<0>();
   __syncthreads();
@@ -247,7 +248,7 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const AttnParams p) {
     const uint32_t ks = kv0 + stage * 2 * KT * LDS * 2, vs = ks + KT * LDS * 2;
     if (tile < tile_hi) {
       const uint32_t nk = kv0 + (stage ^ 1) * 2 * KT * LDS * 2;
-      load_kv_tile(nk, nk + KT * LDS * 2, p.cache, pages[tile + 1], p.n_kv_heads, kvh, tid, 128);
+      load_kv_tile(nk, nk + KT * LDS * 2, p.cache, pages[tile + 1], p.n_kv_heads, kvh, tid, PREFILL_THREADS);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
@@ -505,7 +506,7 @@ extern "C" int sb_attention(const void* q, void* out, int n_rows, int n_seqs, in
   p.n_splits = 1;
   const long tiles = ((long)max_new * G + BM - 1) / BM;
   if (tiles > 2147483647L) SB_FAIL(SB_ERR_UNSUPPORTED, "sb_attention: too many rows");
-  sb_launch(attn_prefill_kernel, dim3((unsigned)tiles, n_kv_heads, n_seqs), dim3(128), PREFILL_SMEM,
+  sb_launch(attn_prefill_kernel, dim3((unsigned)tiles, n_kv_heads, n_seqs), dim3(PREFILL_THREADS), PREFILL_SMEM,
             stream, p);
   SB_CHECK_LAUNCH("sb_attention (prefill)");
   return SB_OK;

@@ -129,34 +129,44 @@ __global__ void rope_store_kernel(const float* qkv, int n_q_heads, int n_kv_head
                                   const int32_t* row_seq, const int32_t* row_pos,
                                   const int32_t* page_off, const int32_t* page_ids,
                                   int page_size, TC* cache, TQ* q_out, int has_kv) {
+  // One block per row: the angles depend on the position and the pair only, so cos and sin
+  // are computed once per row and reused by every head.
+  extern __shared__ float cs[];                      // cos[rot/2], then sin[rot/2]
   sb_pdl_launch();
   sb_pdl_wait();
   const int t = blockIdx.x;
-  const int head = blockIdx.y;                       // q heads, then k heads, then v heads
-  const int width_in = (n_q_heads + (has_kv ? 2 * n_kv_heads : 0)) * hd;
-  const float* src = qkv + (size_t)t * width_in + (size_t)head * hd;
   const int pos = row_pos[t];
   const int half = rot >> 1;
-  const bool is_v = head >= n_q_heads + n_kv_heads;
-
-  for (int e = threadIdx.x; e < hd; e += blockDim.x) {
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    const float theta = (float)pos * inv_freq[i];
+    cs[i] = cosf(theta);
+    cs[half + i] = sinf(theta);
+  }
+  __syncthreads();
+  const int n_heads = n_q_heads + (has_kv ? 2 * n_kv_heads : 0);
+  const float* src_row = qkv + (size_t)t * n_heads * hd;
+  size_t k_base = 0, v_base = 0;
+  if (has_kv) {
+    const int page = page_ids[page_off[row_seq[t]] + pos / page_size];
+    k_base = (((size_t)page * 2) * n_kv_heads * page_size + pos % page_size) * hd;
+    v_base = (((size_t)page * 2 + 1) * n_kv_heads * page_size + pos % page_size) * hd;
+  }
+  for (int idx = threadIdx.x; idx < n_heads * hd; idx += blockDim.x) {
+    const int head = idx / hd, e = idx % hd;       // q heads, then k heads, then v heads
+    const float* src = src_row + (size_t)head * hd;
+    const bool is_v = head >= n_q_heads + n_kv_heads;
     float v = src[e];
     if (!is_v && e < rot) {
       const int i = e < half ? e : e - half;
-      const float theta = (float)pos * inv_freq[i];
-      const float c = cosf(theta), s = sinf(theta);
-      v = e < half ? src[e] * c - src[e + half] * s : src[e - half] * s + src[e] * c;
+      const float c = cs[i], sn = cs[half + i];
+      v = e < half ? src[e] * c - src[e + half] * sn : src[e - half] * sn + src[e] * c;
     }
     if (head < n_q_heads) {
       q_out[((size_t)t * n_q_heads + head) * hd + e] = sb_from_f32<TQ>(v);
+    } else if (is_v) {
+      cache[v_base + (size_t)(head - n_q_heads - n_kv_heads) * page_size * hd + e] = sb_from_f32<TC>(v);
     } else {
-      const int b = row_seq[t];
-      const int page = page_ids[page_off[b] + pos / page_size];
-      const int kvh = is_v ? head - n_q_heads - n_kv_heads : head - n_q_heads;
-      const size_t off =
-          ((((size_t)page * 2 + (is_v ? 1 : 0)) * n_kv_heads + kvh) * page_size + pos % page_size) *
-              hd + e;
-      cache[off] = sb_from_f32<TC>(v);
+      cache[k_base + (size_t)(head - n_q_heads) * page_size * hd + e] = sb_from_f32<TC>(v);
     }
   }
 }
@@ -175,11 +185,13 @@ extern "C" int sb_rope_store(const float* qkv, int n_rows, int n_q_heads, int n_
     SB_FAIL(SB_ERR_ARG, "sb_rope_store: dtype codes %d %d", cache_dtype, q_dtype);
   if (has_kv && (page_size <= 0 || !cache || !page_off || !page_ids))
     SB_FAIL(SB_ERR_ARG, "sb_rope_store: cache arguments missing");
-  const dim3 grid(n_rows, n_q_heads + (has_kv ? 2 * n_kv_heads : 0));
-  const int threads = hd >= 128 ? 128 : (hd >= 64 ? 64 : 32);
+  const dim3 grid(n_rows);
+  const int width = (n_q_heads + (has_kv ? 2 * n_kv_heads : 0)) * hd;
+  const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+  const size_t smem = (size_t)(rot > 0 ? rot : 2) * sizeof(float);
   SB_DISPATCH_DTYPE(q_dtype, TQ, {
     SB_DISPATCH_DTYPE(cache_dtype, TC, {
-      sb_launch(rope_store_kernel<TQ, TC>, grid, dim3(threads), 0, stream,
+      sb_launch(rope_store_kernel<TQ, TC>, grid, dim3(threads), smem, stream,
           qkv, n_q_heads, n_kv_heads, hd, rot, inv_freq, row_seq, row_pos, page_off, page_ids,
           page_size, (TC*)cache, (TQ*)q_out, has_kv);
     });

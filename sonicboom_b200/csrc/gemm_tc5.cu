@@ -268,36 +268,59 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16);
     if (ok && n_k > 0) {
       if (!SWAPPED) {
-        const int m = a_row;
+        // The accumulator is read 32 columns at a time (a thread holds one row), passed through
+        // a 32 x 33 shared-memory tile of this warp (the operand ring is idle by now), and
+        // written out row by row with a lane per column, so that global accesses coalesce.
+        float* stage = reinterpret_cast<float*>(smem_raw + (tiles - raw)) + (warp - 2) * 32 * 33;
+        const int m_base = tile_a * BM + q * 32;
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
           uint32_t r[32];
           tmem_ld32(t_row + c * 32, r);
           const int n0 = tile_b * BN + c * 32;
-          if (m >= p.M || n0 >= p.N) continue;
+          if (n0 >= p.N) break;
+          __syncwarp();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) stage[lane * 33 + j] = __uint_as_float(r[j]);
+          __syncwarp();
           if (p.epilogue == SB_EPI_SWIGLU) {
-            TO* dst = (TO*)p.out + (size_t)m * (p.N / 2) + n0 / 2;
-#pragma unroll
-            for (int blk = 0; blk < 2; ++blk) {
-              if (n0 + blk * 16 >= p.N) break;
-#pragma unroll
-              for (int j = 0; j < 8; ++j)
-                dst[blk * 8 + j] = sb_from_f32<TO>(sb_silu(__uint_as_float(r[blk * 16 + j])) *
-                                                   __uint_as_float(r[blk * 16 + 8 + j]));
+            // 16 outputs per row: lanes 0-15 take an even row, lanes 16-31 the next one
+            const int o = lane & 15, src = (o >> 3) * 16 + (o & 7);
+            const bool live = n0 / 2 + o < p.N / 2;
+#pragma unroll 4
+            for (int rr = 0; rr < 32; rr += 2) {
+              const int row = rr + (lane >> 4), m = m_base + row;
+              if (m < p.M && live)
+                ((TO*)p.out)[(size_t)m * (p.N / 2) + n0 / 2 + o] =
+                    sb_from_f32<TO>(sb_silu(stage[row * 33 + src]) * stage[row * 33 + src + 8]);
             }
             continue;
           }
-          TO* dst = (TO*)p.out + (size_t)m * p.N + n0;
-          const float* res = p.residual ? p.residual + (size_t)m * p.N + n0 : nullptr;
+          const int n = n0 + lane;
+          const bool live = n < p.N;
+          float add = 0.0f;
+          if (p.epilogue == SB_EPI_BIAS && live)
+            add = p.bias_dtype == SB_F32 ? bias_at<float>(p.bias, n) : bias_at<bf16>(p.bias, n);
+          if (p.epilogue == SB_EPI_RESIDUAL) {
+            // every residual value is loaded before any store: the output may be the residual
+            // buffer itself (each element is read and written by the same lane), and loads
+            // that had to stay behind stores would run one at a time
+            float resv[32];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            if (n0 + j >= p.N) break;
-            float v = __uint_as_float(r[j]);
-            if (p.epilogue == SB_EPI_BIAS)
-              v += p.bias_dtype == SB_F32 ? bias_at<float>(p.bias, n0 + j) : bias_at<bf16>(p.bias, n0 + j);
-            else if (p.epilogue == SB_EPI_RESIDUAL)
-              v += res[j];
-            dst[j] = sb_from_f32<TO>(v);
+            for (int rr = 0; rr < 32; ++rr)
+              resv[rr] = (live && m_base + rr < p.M) ? p.residual[(size_t)(m_base + rr) * p.N + n] : 0.0f;
+#pragma unroll
+            for (int rr = 0; rr < 32; ++rr)
+              if (live && m_base + rr < p.M)
+                ((TO*)p.out)[(size_t)(m_base + rr) * p.N + n] =
+                    sb_from_f32<TO>(stage[rr * 33 + lane] + resv[rr]);
+            continue;
+          }
+#pragma unroll 8
+          for (int rr = 0; rr < 32; ++rr) {
+            const int m = m_base + rr;
+            if (m < p.M && live)
+              ((TO*)p.out)[(size_t)m * p.N + n] = sb_from_f32<TO>(stage[rr * 33 + lane] + add);
           }
         }
       } else {
