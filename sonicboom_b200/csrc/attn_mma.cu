@@ -58,6 +58,7 @@ struct AttnParams {
   float* scratch;
   int* counters;               // one per (sequence, key/value head), zero between launches
   int n_q_heads, n_kv_heads, window, n_splits;
+  int n_seqs;
   float scale_log2;            // scale * log2(e)
 };
 
@@ -413,24 +414,56 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(const AttnP
   __syncthreads();
   if (!s_last) return;
   __threadfence();
+  // Final merge.  The splits' (m, l) go to shared memory first, one thread per row turns
+  // them into weights exp2(m_s - max) and the row's 1 / sum, and then every (row, d) is a
+  // weighted sum whose loads are independent of each other and issued four at a time.
+  const int ns = split_hi - split_lo + 1;
+  float* wgt = part;                               // [row][ns]
+  float* den = part + DEC_ROWS * ns;               // [row][ns], then den[row * ns] = 1 / sum
+  for (int i = tid; i < R * ns; i += DEC_WARPS * 32) {
+    const int row = i / ns, sp = split_lo + i % ns;
+    const size_t out_row = (size_t)(row0 + row / G) * p.n_q_heads + kvh * G + row % G;
+    const float* src = p.scratch + (out_row * p.n_splits + sp) * PART_STRIDE;
+    wgt[i] = src[HD];
+    den[i] = src[HD + 1];
+  }
+  __syncthreads();
+  if (tid < R) {
+    float mm = -INFINITY;
+    for (int i = 0; i < ns; ++i) mm = fmaxf(mm, wgt[tid * ns + i]);
+    const float ref = mm == -INFINITY ? 0.0f : mm;
+    float sum = 0.0f;
+    for (int i = 0; i < ns; ++i) {                 // ascending split order
+      const float f = exp2f(wgt[tid * ns + i] - ref);
+      sum += den[tid * ns + i] * f;
+      wgt[tid * ns + i] = f;
+    }
+    den[tid * ns] = 1.0f / sum;
+  }
+  __syncthreads();
   for (int idx = tid; idx < R * HD; idx += DEC_WARPS * 32) {
     const int row = idx / HD, d = idx % HD;
-    const int tok = row / G, g = row % G;
-    const size_t out_row = (size_t)(row0 + tok) * p.n_q_heads + kvh * G + g;
-    const float* base = p.scratch + out_row * p.n_splits * PART_STRIDE;
-    float mm = -INFINITY;
-    for (int s = split_lo; s <= split_hi; ++s) mm = fmaxf(mm, base[(size_t)s * PART_STRIDE + HD]);
-    const float ref = mm == -INFINITY ? 0.0f : mm;
-    float acc = 0.0f, ll = 0.0f;
-    for (int s = split_lo; s <= split_hi; ++s) {
-      const float* src = base + (size_t)s * PART_STRIDE;
-      const float f = exp2f(src[HD] - ref);
-      acc += src[d] * f;
-      ll += src[HD + 1] * f;
+    const size_t out_row = (size_t)(row0 + row / G) * p.n_q_heads + kvh * G + row % G;
+    const float* src = p.scratch + (out_row * p.n_splits + split_lo) * PART_STRIDE + d;
+    const float* w = wgt + row * ns;
+    float acc = 0.0f;
+    int i = 0;
+    for (; i + 4 <= ns; i += 4) {
+      const float v0 = src[(size_t)i * PART_STRIDE], v1 = src[(size_t)(i + 1) * PART_STRIDE];
+      const float v2 = src[(size_t)(i + 2) * PART_STRIDE], v3 = src[(size_t)(i + 3) * PART_STRIDE];
+      acc = fmaf(v0, w[i], acc);
+      acc = fmaf(v1, w[i + 1], acc);
+      acc = fmaf(v2, w[i + 2], acc);
+      acc = fmaf(v3, w[i + 3], acc);
     }
-    p.out[out_row * HD + d] = __float2bfloat16_rn(acc / ll);
+    for (; i < ns; ++i) acc = fmaf(src[(size_t)i * PART_STRIDE], w[i], acc);
+    p.out[out_row * HD + d] = __float2bfloat16_rn(acc * den[row * ns]);
   }
 }
+
+
+// The final merge stages every split's (m, l) of up to 16 rows in the tiles' shared memory.
+constexpr int MAX_MERGE_SPLITS = 4 * LDS;
 
 int n_splits_for(int max_len) { return (max_len + SPLIT_PAGES * KT - 1) / (SPLIT_PAGES * KT); }
 
@@ -442,7 +475,7 @@ extern "C" int sb_attention_head_dim() { return HD; }
 extern "C" size_t sb_attention_scratch_bytes(int n_rows, int n_q_heads, int n_kv_heads, int max_new,
                                              int max_len) {
   const int G = n_q_heads / (n_kv_heads > 0 ? n_kv_heads : 1);
-  if (max_new * G > DEC_ROWS || !DECODE_FITS) return 0;
+  if (max_new * G > DEC_ROWS || !DECODE_FITS || n_splits_for(max_len) > MAX_MERGE_SPLITS) return 0;
   const int n_splits = n_splits_for(max_len);
   if (n_splits <= 1) return 0;
   return (size_t)n_rows * n_q_heads * n_splits * PART_STRIDE * sizeof(float);
@@ -458,7 +491,7 @@ extern "C" int sb_attention(const void* q, void* out, int n_rows, int n_seqs, in
                             const int32_t* page_off, const int32_t* page_ids, int page_size,
                             const void* cache, int n_q_heads, int n_kv_heads, int hd, int window,
                             float scale, void* scratch, size_t scratch_bytes, int* counters,
-                            int n_counters, int max_len, cudaStream_t stream) {
+                            int n_counters, int max_len, int n_sms, cudaStream_t stream) {
   if (hd != HD) SB_FAIL(SB_ERR_ARG, "sb_attention: built for head size %d, called with %d", HD, hd);
   if (page_size != KT)
     SB_FAIL(SB_ERR_UNSUPPORTED, "sb_attention: cache pages of %d keys (needs %d)", page_size, KT);
@@ -475,7 +508,7 @@ extern "C" int sb_attention(const void* q, void* out, int n_rows, int n_seqs, in
   p.q = (const bf16*)q; p.out = (bf16*)out;
   p.seq_row0 = seq_row0; p.seq_pos0 = seq_pos0; p.page_off = page_off; p.page_ids = page_ids;
   p.cache = (const bf16*)cache; p.scratch = (float*)scratch; p.counters = counters;
-  p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads; p.window = window;
+  p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads; p.window = window; p.n_seqs = n_seqs;
   p.scale_log2 = scale * LOG2E;
   const int G = n_q_heads / n_kv_heads;
   static bool configured = false;
@@ -490,7 +523,7 @@ extern "C" int sb_attention(const void* q, void* out, int n_rows, int n_seqs, in
               cudaGetErrorString(e1 != cudaSuccess ? e1 : e2));
     configured = true;
   }
-  if (max_new * G <= DEC_ROWS && DECODE_FITS) {
+  if (max_new * G <= DEC_ROWS && DECODE_FITS && n_splits_for(max_len) <= MAX_MERGE_SPLITS) {
     p.n_splits = n_splits_for(max_len);
     const size_t need = sb_attention_scratch_bytes(n_rows, n_q_heads, n_kv_heads, max_new, max_len);
     if (need > scratch_bytes || (need && !scratch))
@@ -552,10 +585,11 @@ extern "C" int sb_attention_decode_static(const void* q, void* out, int n_rows, 
     SB_FAIL(SB_ERR_UNSUPPORTED, "%s: %d/%d heads, %d sequences", who, n_q_heads, n_kv_heads, n_seqs);
   if (((uintptr_t)q | (uintptr_t)cache) & 15) SB_FAIL(SB_ERR_ARG, "%s: unaligned operands", who);
   const int G = n_q_heads / n_kv_heads;
-  if (max_new * G > DEC_ROWS || !DECODE_FITS)
+  if (max_new * G > DEC_ROWS || !DECODE_FITS || n_splits_for(max_len) > MAX_MERGE_SPLITS)
     SB_FAIL(SB_ERR_UNSUPPORTED,
-            "%s: decode steps only (%d new rows x %d heads per group is above %d rows, or the "
-            "head size is too large for the decode kernel)", who, max_new, G, DEC_ROWS);
+            "%s: decode steps only (%d new rows x %d heads per group is above %d rows, the head "
+            "size is too large for the decode kernel, or max_len %d is above %d splits)", who,
+            max_new, G, DEC_ROWS, max_len, MAX_MERGE_SPLITS);
   const int n_splits = n_splits_for(max_len);
   const size_t need = (size_t)n_rows * n_q_heads * n_splits * PART_STRIDE * sizeof(float);
   if ((long)n_seqs * n_kv_heads > STATIC_COUNTERS)
@@ -595,6 +629,7 @@ extern "C" int sb_attention_decode_static(const void* q, void* out, int n_rows, 
   p.cache = (const bf16*)cache; p.scratch = g_static_scratch_ptr[device];
   p.counters = g_static_counters_ptr[device];
   p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads; p.window = window; p.n_splits = n_splits;
+  p.n_seqs = n_seqs;
   p.scale_log2 = scale * LOG2E;
   sb_launch(attn_decode_kernel, dim3(n_splits, n_kv_heads, n_seqs), dim3(DEC_WARPS * 32), DECODE_SMEM,
             stream, p);

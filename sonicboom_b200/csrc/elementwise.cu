@@ -123,6 +123,42 @@ extern "C" int sb_cast(const void* in, int in_dtype, void* out, int out_dtype, s
 //
 // Cache of one schedule entry: [page][k|v][kv head][slot in page][hd].  The page of position p
 // of sequence b is page_ids[page_off[b] + p / page_size].
+// Few rows (decode): one block per (row, head), so that even one row spreads over many SMs.
+template <typename TQ, typename TC>
+__global__ void rope_store_head_kernel(const float* qkv, int n_q_heads, int n_kv_heads, int hd,
+                                       int rot, const float* __restrict__ inv_freq,
+                                       const int32_t* row_seq, const int32_t* row_pos,
+                                       const int32_t* page_off, const int32_t* page_ids,
+                                       int page_size, TC* cache, TQ* q_out, int has_kv) {
+  sb_pdl_launch();
+  sb_pdl_wait();
+  const int t = blockIdx.x;
+  const int head = blockIdx.y;                       // q heads, then k heads, then v heads
+  const int width_in = (n_q_heads + (has_kv ? 2 * n_kv_heads : 0)) * hd;
+  const float* src = qkv + (size_t)t * width_in + (size_t)head * hd;
+  const int pos = row_pos[t];
+  const int half = rot >> 1;
+  const bool is_v = head >= n_q_heads + n_kv_heads;
+  for (int e = threadIdx.x; e < hd; e += blockDim.x) {
+    float v = src[e];
+    if (!is_v && e < rot) {
+      const int i = e < half ? e : e - half;
+      const float theta = (float)pos * inv_freq[i];
+      const float c = cosf(theta), sn = sinf(theta);
+      v = e < half ? src[e] * c - src[e + half] * sn : src[e - half] * sn + src[e] * c;
+    }
+    if (head < n_q_heads) {
+      q_out[((size_t)t * n_q_heads + head) * hd + e] = sb_from_f32<TQ>(v);
+    } else {
+      const int page = page_ids[page_off[row_seq[t]] + pos / page_size];
+      const int kvh = is_v ? head - n_q_heads - n_kv_heads : head - n_q_heads;
+      cache[((((size_t)page * 2 + (is_v ? 1 : 0)) * n_kv_heads + kvh) * page_size + pos % page_size) *
+                hd + e] = sb_from_f32<TC>(v);
+    }
+  }
+}
+
+// Many rows (prefill):
 template <typename TQ, typename TC>
 __global__ void rope_store_kernel(const float* qkv, int n_q_heads, int n_kv_heads,
                                   int hd, int rot, const float* __restrict__ inv_freq,
@@ -189,6 +225,19 @@ extern "C" int sb_rope_store(const float* qkv, int n_rows, int n_q_heads, int n_
   const int width = (n_q_heads + (has_kv ? 2 * n_kv_heads : 0)) * hd;
   const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
   const size_t smem = (size_t)(rot > 0 ? rot : 2) * sizeof(float);
+  if (n_rows < 64 && n_q_heads + 2 * n_kv_heads <= 65535) {
+    const dim3 hgrid(n_rows, n_q_heads + (has_kv ? 2 * n_kv_heads : 0));
+    const int hthreads = hd >= 128 ? 128 : (hd >= 64 ? 64 : 32);
+    SB_DISPATCH_DTYPE(q_dtype, TQ, {
+      SB_DISPATCH_DTYPE(cache_dtype, TC, {
+        sb_launch(rope_store_head_kernel<TQ, TC>, hgrid, dim3(hthreads), 0, stream, qkv, n_q_heads,
+                  n_kv_heads, hd, rot, inv_freq, row_seq, row_pos, page_off, page_ids, page_size,
+                  (TC*)cache, (TQ*)q_out, has_kv);
+      });
+    });
+    SB_CHECK_LAUNCH("sb_rope_store");
+    return SB_OK;
+  }
   SB_DISPATCH_DTYPE(q_dtype, TQ, {
     SB_DISPATCH_DTYPE(cache_dtype, TC, {
       sb_launch(rope_store_kernel<TQ, TC>, grid, dim3(threads), smem, stream,

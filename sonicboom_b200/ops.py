@@ -274,7 +274,7 @@ def attention(q: torch.Tensor, out: torch.Tensor, plan, group_index: int, cache:
             _i32(g.page_ids, "page_ids"), g.page_size, _ptr(cache), n_q_heads, n_kv_heads,
             head_dim, window, ctypes.c_float(scale), _ptr(scratch),
             ctypes.c_size_t(scratch.numel() if scratch is not None else 0),
-            _ptr(counters), counters.numel(), plan.max_len, _stream())
+            _ptr(counters), counters.numel(), plan.max_len, _sm_count(q.device), _stream())
         if rc != 0:
             raise KernelError(f"attention: {al.sb_last_error().decode()}")
         global LAUNCHES

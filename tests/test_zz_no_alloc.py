@@ -62,9 +62,9 @@ def test_static_scratch_entry_point_matches_the_ordinary_one():
         assert torch.equal(got, want), (call, float((got.float() - want.float()).abs().max()))
 
     # a step beyond the built-in array is refused before anything runs, with both numbers in
-    # the message (the bound on the sequence length alone decides this)
-    rc = fn(ptr(q), ptr(got), len(lengths), plan.n_seqs, plan.max_new, ptr(plan.seq_row0),
+    # the message (the bounds on rows and sequence length alone decide this)
+    rc = fn(ptr(q), ptr(got), 4096, plan.n_seqs, plan.max_new, ptr(plan.seq_row0),
             ptr(plan.seq_pos0), ptr(g.page_off), ptr(g.page_ids), g.page_size, ptr(storage), hq, hkv,
-            hd, 0, ctypes.c_float(hd ** -0.5), 40_000_000, stream)
+            hd, 0, ctypes.c_float(hd ** -0.5), 16000, stream)
     msg = lib.sb_last_error().decode()
     assert rc != 0 and "8388608" in msg and "scratch" in msg, msg
