@@ -41,7 +41,10 @@ constexpr int LDS = HD + 8;            // shared-memory row stride: an odd numbe
 constexpr int BM = HD <= 128 ? 128 : 64;  // prefill rows per block (16 per warp); registers bound it
 constexpr int PREFILL_THREADS = BM / 16 * 32;
 constexpr int DEC_WARPS = 4;           // decode: warps per block, 16 keys of every tile each
-constexpr int SPLIT_PAGES = 4;         // decode: pages per split (256 keys)
+#ifndef SB_SPLIT_PAGES
+#define SB_SPLIT_PAGES 4
+#endif
+constexpr int SPLIT_PAGES = SB_SPLIT_PAGES;  // decode: pages per split (256 keys)
 constexpr int DEC_ROWS = 16;
 constexpr float LOG2E = 1.4426950408889634f;
 

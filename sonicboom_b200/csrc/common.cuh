@@ -66,8 +66,8 @@ __device__ __forceinline__ float sb_warp_max(float v) {
   return v;
 }
 
-// Programmatic dependent launch: every kernel of a step is launched so that it may start
-// while its predecessor in the stream is still running.  A kernel calls sb_pdl_launch() early
+// Programmatic dependent launch (optional, see sb_pdl_enabled): every kernel of a step can be
+// launched so that it may start while its predecessor in the stream is still running.  A kernel calls sb_pdl_launch() early
 // (its successor may then be scheduled as soon as resources free up) and sb_pdl_wait() before
 // it first touches anything a predecessor wrote; what it does before the wait (barrier set-up,
 // prefetching weights) overlaps the predecessor's tail.  Without the launch attribute both are

@@ -17,13 +17,16 @@ void sb_set_error(const char* fmt, ...) {
 }
 
 
-// Whether kernels are launched with programmatic dependent launch (on unless SB_PDL=0).
+// Whether kernels are launched with programmatic dependent launch.  Off unless SB_PDL=1: on
+// B200 the decode step of the 7B-sized model measured slower with it (the many small blocks of
+// the weight-streaming product gain nothing from starting early and delay their neighbours),
+// while the tcgen05 products alone gain a few percent.
 static int g_pdl = -1;
 
 extern "C" int sb_pdl_enabled() {
   if (g_pdl < 0) {
     const char* e = getenv("SB_PDL");
-    g_pdl = (e && e[0] == '0') ? 0 : 1;
+    g_pdl = (e && e[0] == '1') ? 1 : 0;
   }
   return g_pdl;
 }

@@ -150,6 +150,9 @@ def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = 
     return out
 
 
+FORCE_DECODE_KERNEL = None      # "skinny" or "tc5": overrides the choice below (for measurements)
+
+
 def _pick_kernel(M: int, N: int, K: int, device) -> str:
     """Which bfloat16 product kernel "auto" means.  Above SKINNY_MAX_ROWS rows: the tcgen05
     kernel.  Up to that many rows the product is bound by reading W once: the tcgen05 kernel
@@ -158,6 +161,8 @@ def _pick_kernel(M: int, N: int, K: int, device) -> str:
     small matrices (measured on B200 at the 7B layer sizes)."""
     if M > SKINNY_MAX_ROWS:
         return "tc5"
+    if FORCE_DECODE_KERNEL:
+        return FORCE_DECODE_KERNEL
     tiles = (N + 127) // 128
     if tiles >= _sm_count(device) or (K >= 8192 and M <= 32):
         return "tc5"
@@ -192,8 +197,8 @@ def _tc5_workspace(M: int, N: int, K: int, device):
 
 
 def set_pdl(on: bool) -> None:
-    """Turns programmatic dependent launch of the kernels on or off (on by default; the
-    environment variable SB_PDL=0 turns it off at start)."""
+    """Turns programmatic dependent launch of the kernels on or off (off by default; the
+    environment variable SB_PDL=1 turns it on at start)."""
     lib().sb_set_pdl(1 if on else 0)
     for l in _attn_libs.values():
         if l is not None:
