@@ -159,7 +159,7 @@ def run(args) -> int:
         return [torch.randint(0, cfg["vocab_size"], (PROMPT_LEN,), generator=gen).tolist()
                 for _ in range(n)]
 
-    def decode_point(batch, steps, warmup, clocks=None):
+    def decode_point(batch, steps, warmup, clocks=None, graph=True):
         """Prefills `batch` prompts (8 at a time), then times `steps` steps of the decode loop
         on the device with CUDA events."""
         engine = sb.Engine(model, max_tokens=batch * CONTEXT, n_slots=batch)
@@ -178,7 +178,7 @@ def run(args) -> int:
         for s in slots:
             engine.cache.reserve(s, PROMPT_LEN + skip)
             engine.cache.advance(s, PROMPT_LEN + skip)
-        loop = DecodeLoop(engine, slots, max_new=warmup + steps + 2)
+        loop = DecodeLoop(engine, slots, max_new=warmup + steps + 2, use_graph=graph)
         loop.run_device(first, warmup)
         torch.cuda.synchronize()
         ctx_start = engine.length(slots[0]) + warmup
@@ -223,6 +223,13 @@ def run(args) -> int:
         torch.cuda.empty_cache()
         return {"tok_s": batch * steps / dt, "h2d": 4 * batch, "d2h": 4 * batch}
 
+    if args.only == "decode":
+        # a small case for profilers: the decode point alone (with --eager: kernel by kernel)
+        r = decode_point(args.batch, args.steps, args.warmup, graph=not args.eager)
+        print(json.dumps({"only": "decode", "layers": cfg["num_hidden_layers"], "batch": args.batch,
+                          "ms_per_step": round(r["ms_per_step"], 4), "tok_s": round(r["tok_s"], 1)}))
+        return 0
+
     # prefill of one 2,048-token prompt
     engine = sb.Engine(model, max_tokens=PROMPT_LEN, n_slots=1)
     (p,) = prompts(1)
@@ -243,6 +250,10 @@ def run(args) -> int:
         cfg["num_hidden_layers"] * 4 * cfg["num_attention_heads"] * hd * PROMPT_LEN * PROMPT_LEN / 2 + \
         2 * cfg["hidden_size"] * cfg["vocab_size"]
     del engine
+    if args.only == "prefill":
+        print(json.dumps({"only": "prefill", "layers": cfg["num_hidden_layers"], "tokens": PROMPT_LEN,
+                          "ms": round(prefill_ms, 3)}))
+        return 0
 
     clocks = ClockSampler()
     main = decode_point(args.batch, args.steps, args.warmup, clocks=clocks)
@@ -292,6 +303,10 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=0,
                     help="run fewer layers than the model has (both numbers go into config)")
     ap.add_argument("--prefill-reps", type=int, default=3)
+    ap.add_argument("--only", choices=["decode", "prefill"], default=None,
+                    help="run one phase only and print a short line (small cases for profilers)")
+    ap.add_argument("--eager", action="store_true",
+                    help="with --only decode: launch the step kernel by kernel, not as a graph")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
