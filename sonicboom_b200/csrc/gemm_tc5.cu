@@ -153,6 +153,56 @@ struct Tc5Params {
 constexpr int stage_bytes(int bn) { return (BM + bn) * BK * 2; }
 constexpr int smem_bytes(int bn, int stages) { return stages * stage_bytes(bn) + 1024 + 256; }
 
+// Epilogue of one 32-row x 32-column chunk of the normal form.  The accumulator chunk (a thread
+// holds one row) is passed through a 32 x 33 shared-memory tile of the warp and written out row
+// by row with a lane per column, so that global accesses coalesce.
+template <typename TO>
+__device__ __forceinline__ void store_chunk(const Tc5Params& p, float* stage, const uint32_t (&r)[32],
+                                            int m_base, int n0, int lane) {
+  __syncwarp();
+#pragma unroll
+  for (int j = 0; j < 32; ++j) stage[lane * 33 + j] = __uint_as_float(r[j]);
+  __syncwarp();
+  if (p.epilogue == SB_EPI_SWIGLU) {
+    // 16 outputs per row: lanes 0-15 take an even row, lanes 16-31 the next one
+    const int o = lane & 15, src = (o >> 3) * 16 + (o & 7);
+    const bool live = n0 / 2 + o < p.N / 2;
+#pragma unroll 4
+    for (int rr = 0; rr < 32; rr += 2) {
+      const int row = rr + (lane >> 4), m = m_base + row;
+      if (m < p.M && live)
+        ((TO*)p.out)[(size_t)m * (p.N / 2) + n0 / 2 + o] =
+            sb_from_f32<TO>(sb_silu(stage[row * 33 + src]) * stage[row * 33 + src + 8]);
+    }
+    return;
+  }
+  const int n = n0 + lane;
+  const bool live = n < p.N;
+  float add = 0.0f;
+  if (p.epilogue == SB_EPI_BIAS && live)
+    add = p.bias_dtype == SB_F32 ? bias_at<float>(p.bias, n) : bias_at<bf16>(p.bias, n);
+  if (p.epilogue == SB_EPI_RESIDUAL) {
+    // every residual value is loaded before any store: the output may be the residual
+    // buffer itself (each element is read and written by the same lane), and loads
+    // that had to stay behind stores would run one at a time
+    float resv[32];
+#pragma unroll
+    for (int rr = 0; rr < 32; ++rr)
+      resv[rr] = (live && m_base + rr < p.M) ? p.residual[(size_t)(m_base + rr) * p.N + n] : 0.0f;
+#pragma unroll
+    for (int rr = 0; rr < 32; ++rr)
+      if (live && m_base + rr < p.M)
+        ((TO*)p.out)[(size_t)(m_base + rr) * p.N + n] = sb_from_f32<TO>(stage[rr * 33 + lane] + resv[rr]);
+    return;
+  }
+#pragma unroll 8
+  for (int rr = 0; rr < 32; ++rr) {
+    const int m = m_base + rr;
+    if (m < p.M && live)
+      ((TO*)p.out)[(size_t)m * p.N + n] = sb_from_f32<TO>(stage[rr * 33 + lane] + add);
+  }
+}
+
 // ----------------------------------------------------------------------------- the kernel
 // SWAPPED = false: A rows are tokens (m), B rows are features (n).
 // SWAPPED = true:  A rows are features (n), B rows are tokens (m <= BN).
@@ -268,9 +318,6 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16);
     if (ok && n_k > 0) {
       if (!SWAPPED) {
-        // The accumulator is read 32 columns at a time (a thread holds one row), passed through
-        // a 32 x 33 shared-memory tile of this warp (the operand ring is idle by now), and
-        // written out row by row with a lane per column, so that global accesses coalesce.
         float* stage = reinterpret_cast<float*>(smem_raw + (tiles - raw)) + (warp - 2) * 32 * 33;
         const int m_base = tile_a * BM + q * 32;
 #pragma unroll 1
@@ -279,49 +326,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           tmem_ld32(t_row + c * 32, r);
           const int n0 = tile_b * BN + c * 32;
           if (n0 >= p.N) break;
-          __syncwarp();
-#pragma unroll
-          for (int j = 0; j < 32; ++j) stage[lane * 33 + j] = __uint_as_float(r[j]);
-          __syncwarp();
-          if (p.epilogue == SB_EPI_SWIGLU) {
-            // 16 outputs per row: lanes 0-15 take an even row, lanes 16-31 the next one
-            const int o = lane & 15, src = (o >> 3) * 16 + (o & 7);
-            const bool live = n0 / 2 + o < p.N / 2;
-#pragma unroll 4
-            for (int rr = 0; rr < 32; rr += 2) {
-              const int row = rr + (lane >> 4), m = m_base + row;
-              if (m < p.M && live)
-                ((TO*)p.out)[(size_t)m * (p.N / 2) + n0 / 2 + o] =
-                    sb_from_f32<TO>(sb_silu(stage[row * 33 + src]) * stage[row * 33 + src + 8]);
-            }
-            continue;
-          }
-          const int n = n0 + lane;
-          const bool live = n < p.N;
-          float add = 0.0f;
-          if (p.epilogue == SB_EPI_BIAS && live)
-            add = p.bias_dtype == SB_F32 ? bias_at<float>(p.bias, n) : bias_at<bf16>(p.bias, n);
-          if (p.epilogue == SB_EPI_RESIDUAL) {
-            // every residual value is loaded before any store: the output may be the residual
-            // buffer itself (each element is read and written by the same lane), and loads
-            // that had to stay behind stores would run one at a time
-            float resv[32];
-#pragma unroll
-            for (int rr = 0; rr < 32; ++rr)
-              resv[rr] = (live && m_base + rr < p.M) ? p.residual[(size_t)(m_base + rr) * p.N + n] : 0.0f;
-#pragma unroll
-            for (int rr = 0; rr < 32; ++rr)
-              if (live && m_base + rr < p.M)
-                ((TO*)p.out)[(size_t)(m_base + rr) * p.N + n] =
-                    sb_from_f32<TO>(stage[rr * 33 + lane] + resv[rr]);
-            continue;
-          }
-#pragma unroll 8
-          for (int rr = 0; rr < 32; ++rr) {
-            const int m = m_base + rr;
-            if (m < p.M && live)
-              ((TO*)p.out)[(size_t)m * p.N + n] = sb_from_f32<TO>(stage[rr * 33 + lane] + add);
-          }
+          store_chunk<TO>(p, stage, r, m_base, n0, lane);
         }
       } else {
         // swapped: this thread owns feature n = a_row and holds its value for every token
@@ -406,6 +411,138 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   }
 }
 
+// ------------------------------------------------------------------ the persistent kernel
+// Normal form only.  One block per SM walks its tiles (block b takes tiles b, b + grid, ...; a
+// tile index walks the A tiles of one B tile first, so that the blocks of a wave share operand
+// tiles through L2).  Tiles are 128 x BN with BN up to 256, which halves the operand traffic per
+// flop of the 128 x 128 kernel; tensor memory holds two accumulators, so the epilogue of a tile
+// runs while the MMAs of the block's next tile are already being issued.
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+}
+
+constexpr int PERSIST_STAGING = 4 * 32 * 33 * 4;     // the epilogue warps' transpose tiles
+constexpr int persist_smem_bytes(int bn, int stages) {
+  return stages * stage_bytes(bn) + PERSIST_STAGING + 1024 + 256;
+}
+
+template <int BN, int STAGES, typename TO>
+__global__ void __launch_bounds__(THREADS)
+gemm_tc5_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
+                           const __grid_constant__ CUtensorMap map_b, const Tc5Params p) {
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t raw = (uint32_t)__cvta_generic_to_shared(smem_raw);
+  const uint32_t tiles = (raw + 1023u) & ~1023u;
+  const uint32_t staging = tiles + STAGES * stage_bytes(BN);
+  const uint32_t bars = staging + PERSIST_STAGING;
+  const uint32_t full0 = bars, empty0 = bars + 8 * STAGES;
+  const uint32_t acc_full0 = bars + 16 * STAGES, acc_empty0 = acc_full0 + 16;
+  const uint32_t tmem_slot = acc_empty0 + 16;
+  volatile uint32_t* tmem_slot_ptr = (volatile uint32_t*)(smem_raw + (tmem_slot - raw));
+  constexpr uint32_t ACC_COLS = 256;                   // column offset of the second accumulator
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  sb_pdl_launch();
+  const int n_tiles = p.tiles_a * p.tiles_b;
+  const int n_k = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full0 + 8 * s, 1);
+      mbar_init(empty0 + 8 * s, 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(acc_full0 + 8 * a, 1);
+      mbar_init(acc_empty0 + 8 * a, 4);                // one arrival per epilogue warp
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+
+  if (warp == 0 && lane == 0) {
+    // ---- producer
+    sb_pdl_wait();
+    uint32_t it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+      const int tile_a = tile % p.tiles_a, tile_b = tile / p.tiles_a;
+      for (int kt = 0; kt < n_k; ++kt, ++it) {
+        const uint32_t s = it % STAGES;
+        ok = mbar_wait(empty0 + 8 * s, ((it / STAGES) & 1) ^ 1, 1);
+        if (!ok) break;
+        mbar_expect_tx(full0 + 8 * s, stage_bytes(BN));
+        const uint32_t a_dst = tiles + s * stage_bytes(BN), b_dst = a_dst + BM * BK * 2;
+        tma_load_2d(a_dst, &map_a, kt * BK, tile_a * BM, full0 + 8 * s);
+        tma_load_2d(b_dst, &map_b, kt * BK, tile_b * BN, full0 + 8 * s);
+      }
+    }
+    if (!ok) {
+      // let copies that are still in flight land before the block's memory goes away
+      for (uint32_t i = it > STAGES ? it - STAGES : 0; i < it; ++i)
+        mbar_wait(full0 + 8 * (i % STAGES), (i / STAGES) & 1, 2);
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ---- MMA issuer
+    constexpr uint32_t idesc = instr_desc(BN);
+    uint32_t it = 0, lt = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++lt) {
+      const uint32_t acc = lt & 1;
+      ok = mbar_wait(acc_empty0 + 8 * acc, ((lt >> 1) & 1) ^ 1, 5);   // the epilogue has drained it
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + acc * ACC_COLS;
+      for (int kt = 0; kt < n_k; ++kt, ++it) {
+        const uint32_t s = it % STAGES;
+        ok = mbar_wait(full0 + 8 * s, (it / STAGES) & 1, 3);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t a_addr = tiles + s * stage_bytes(BN), b_addr = a_addr + BM * BK * 2;
+        const uint64_t adesc = smem_desc(a_addr), bdesc = smem_desc(b_addr);
+#pragma unroll
+        for (int k = 0; k < BK / UMMA_K; ++k)
+          umma_bf16(d_tmem, adesc + (uint64_t)(k * UMMA_K * 2 >> 4),
+                    bdesc + (uint64_t)(k * UMMA_K * 2 >> 4), idesc, (kt > 0 || k > 0) ? 1u : 0u);
+        umma_commit(empty0 + 8 * s);
+      }
+      umma_commit(acc_full0 + 8 * acc);
+    }
+  } else if (warp >= 2) {
+    // ---- epilogue: this warp reads TMEM lanes [32 q, 32 q + 32) of the finished accumulator
+    sb_pdl_wait();
+    const int q = warp & 3;
+    float* stage = reinterpret_cast<float*>(smem_raw + (staging - raw)) + (warp - 2) * 32 * 33;
+    uint32_t lt = 0;
+    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++lt) {
+      const int tile_a = tile % p.tiles_a, tile_b = tile / p.tiles_a;
+      const uint32_t acc = lt & 1;
+      if (!mbar_wait(acc_full0 + 8 * acc, (lt >> 1) & 1, 4)) break;
+      tc_fence_after();
+      const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + acc * ACC_COLS;
+      const int m_base = tile_a * BM + q * 32;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(t_row + c * 32, r);
+        const int n0 = tile_b * BN + c * 32;
+        if (n0 < p.N) store_chunk<TO>(p, stage, r, m_base, n0, lane);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty0 + 8 * acc);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, 512);
+}
+
 // --------------------------------------------------------------------------- host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
@@ -453,6 +590,37 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const Tc5Params& p, int
             mb, p);
   SB_CHECK_LAUNCH("sb_gemm_tc5");
   return SB_OK;
+}
+
+template <int BN, int STAGES, typename TO>
+int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, const Tc5Params& p, int blocks,
+                      cudaStream_t stream) {
+  static bool configured = false;
+  constexpr int smem = persist_smem_bytes(BN, STAGES);
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc5_persistent_kernel<BN, STAGES, TO>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess)
+      SB_FAIL(SB_ERR_CUDA, "sb_gemm_tc5: shared memory opt-in failed: %s", cudaGetErrorString(e));
+    configured = true;
+  }
+  sb_launch(gemm_tc5_persistent_kernel<BN, STAGES, TO>, dim3(blocks), dim3(THREADS), smem, stream, ma,
+            mb, p);
+  SB_CHECK_LAUNCH("sb_gemm_tc5 (persistent)");
+  return SB_OK;
+}
+
+// Tile width of the persistent kernel: the candidate that needs the least (waves x width).
+int persistent_bn(int M, int N, int n_sms) {
+  const int tiles_m = (M + BM - 1) / BM;
+  int best = 0;
+  long best_cost = 0;
+  for (int bn : {256, 224}) {
+    const long tiles = (long)tiles_m * ((N + bn - 1) / bn);
+    const long cost = ((tiles + n_sms - 1) / n_sms) * bn;
+    if (!best || cost < best_cost) { best = bn; best_cost = cost; }
+  }
+  return best;
 }
 
 }  // namespace
@@ -517,6 +685,23 @@ extern "C" int sb_gemm_tc5(const void* A, int a_dtype, const void* W, int w_dtyp
   p.M = M; p.N = N; p.K = K; p.epilogue = epilogue; p.bias = bias; p.bias_dtype = bias_dtype;
   p.residual = residual; p.out = out; p.k_splits = 1; p.scratch = nullptr; p.counters = nullptr;
   CUtensorMap ma, mb;
+  if (M > 64 && N >= 224 && n_sms > 0) {
+    // many rows, wide output: the persistent kernel
+    const int bn = persistent_bn(M, N, n_sms);
+    p.tiles_a = (M + BM - 1) / BM;
+    p.tiles_b = (N + bn - 1) / bn;
+    if (!make_map(&ma, A, M, K, BM) || !make_map(&mb, W, N, K, bn))
+      SB_FAIL(SB_ERR_CUDA, "sb_gemm_tc5: cuTensorMapEncodeTiled failed");
+    const long n_tiles = (long)p.tiles_a * p.tiles_b;
+    if (n_tiles > 2147483647L) SB_FAIL(SB_ERR_UNSUPPORTED, "sb_gemm_tc5: too many tiles");
+    const int blocks = (int)(n_tiles < n_sms ? n_tiles : n_sms);
+    if (bn == 256) {
+      if (out_dtype == SB_F32) return launch_persistent<256, 4, float>(ma, mb, p, blocks, stream);
+      return launch_persistent<256, 4, bf16>(ma, mb, p, blocks, stream);
+    }
+    if (out_dtype == SB_F32) return launch_persistent<224, 4, float>(ma, mb, p, blocks, stream);
+    return launch_persistent<224, 4, bf16>(ma, mb, p, blocks, stream);
+  }
   if (M > 64) {
     constexpr int BN = 128;
     p.tiles_a = (M + BM - 1) / BM;
