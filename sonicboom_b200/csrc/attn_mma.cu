@@ -318,7 +318,16 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(const AttnP
     cp_async16(qs + (uint32_t)(row * LDS + ch * 8) * 2,
                p.q + ((size_t)(row0 + t) * p.n_q_heads + kvh * G + g) * HD + ch * 8, valid);
   }
-  load_kv_tile(kv0, kv0 + KT * LDS * 2, p.cache, pages[tile_lo], p.n_kv_heads, kvh, tid, DEC_WARPS * 32);
+  // the split's page ids are read together, and its first two tiles are requested at once
+  int page_of[SPLIT_PAGES];
+#pragma unroll
+  for (int i = 0; i < SPLIT_PAGES; ++i)
+    page_of[i] = tile_lo + i <= tile_hi ? pages[tile_lo + i] : 0;
+  load_kv_tile(kv0, kv0 + KT * LDS * 2, p.cache, page_of[0], p.n_kv_heads, kvh, tid, DEC_WARPS * 32);
+  cp_async_commit();
+  if (tile_lo < tile_hi)
+    load_kv_tile(kv0 + 2 * KT * LDS * 2, kv0 + 3 * KT * LDS * 2, p.cache, page_of[1], p.n_kv_heads, kvh,
+                 tid, DEC_WARPS * 32);
   cp_async_commit();
 
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
@@ -334,21 +343,22 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(const AttnP
   for (int tile = tile_lo; tile <= tile_hi; ++tile) {
     const int stage = (tile - tile_lo) & 1;
     const uint32_t ks = kv0 + stage * 2 * KT * LDS * 2, vs = ks + KT * LDS * 2;
-    if (tile < tile_hi) {
-      const uint32_t nk = kv0 + (stage ^ 1) * 2 * KT * LDS * 2;
-      load_kv_tile(nk, nk + KT * LDS * 2, p.cache, pages[tile + 1], p.n_kv_heads, kvh, tid, DEC_WARPS * 32);
-      cp_async_commit();
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
-    }
+    cp_async_wait<1>();                               // this tile has landed; the next may be in flight
     __syncthreads();
     if (tile == tile_lo) load_q_frags(qs, 0, lane, qf);
     // this warp's 16 keys of the tile
     const uint32_t off = (uint32_t)(warp * 16 * LDS) * 2;
     tile_step<16>(qf, ks + off, vs + off, tile * KT + warp * 16, pos_a, pos_b, p.window, p.scale_log2,
                   m, l, o, lane);
-    __syncthreads();
+    __syncthreads();                                  // the stage is free: request the tile after next
+    if (tile + 2 <= tile_hi) {
+      int pg = page_of[0];
+#pragma unroll
+      for (int i = 1; i < SPLIT_PAGES; ++i)
+        if (tile + 2 - tile_lo == i) pg = page_of[i];
+      load_kv_tile(ks, vs, p.cache, pg, p.n_kv_heads, kvh, tid, DEC_WARPS * 32);
+    }
+    cp_async_commit();
   }
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
@@ -419,7 +429,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(const AttnP
   __threadfence();
   // Final merge.  The splits' (m, l) go to shared memory first, one thread per row turns
   // them into weights exp2(m_s - max) and the row's 1 / sum, and then every (row, d) is a
-  // weighted sum whose loads are independent of each other and issued four at a time.
+  // weighted sum whose loads are independent of each other and issued eight at a time.
   const int ns = split_hi - split_lo + 1;
   float* wgt = part;                               // [row][ns]
   float* den = part + DEC_ROWS * ns;               // [row][ns], then den[row * ns] = 1 / sum
@@ -451,6 +461,13 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(const AttnP
     const float* w = wgt + row * ns;
     float acc = 0.0f;
     int i = 0;
+    for (; i + 8 <= ns; i += 8) {
+      float v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = src[(size_t)(i + u) * PART_STRIDE];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) acc = fmaf(v[u], w[i + u], acc);
+    }
     for (; i + 4 <= ns; i += 4) {
       const float v0 = src[(size_t)i * PART_STRIDE], v1 = src[(size_t)(i + 1) * PART_STRIDE];
       const float v2 = src[(size_t)(i + 2) * PART_STRIDE], v3 = src[(size_t)(i + 3) * PART_STRIDE];
