@@ -12,9 +12,8 @@
 //   normal   A = activations (rows are tokens), B = weights: the prefill product;
 //   swapped  A = weights (128 weight rows per tile), B = activations (up to 64 rows): the
 //            decode product, which is bound by reading the weights once.  K may be split over
-//            several blocks; their partial tiles go to scratch memory and the block that
-//            arrives last adds them in split order and runs the epilogue, so the sum's order
-//            is fixed.
+//            several blocks; their partial tiles go to scratch memory and a second kernel adds
+//            them in split order and runs the epilogue, so the sum's order is fixed.
 //
 // Every wait on an mbarrier is bounded; when a bound is hit the kernel records a code in a
 // status word, stops issuing work and leaves normally (sb_tc5_status reads the word).
@@ -146,8 +145,7 @@ struct Tc5Params {
   void* out;
   int tiles_a, tiles_b;        // tiles along the A rows and along the B rows
   int k_splits;                // swapped form: blocks that share one output tile
-  float* scratch;              // swapped form with k_splits > 1: [tile][split][BN][128] floats
-  int* counters;               // one per output tile, zero between launches
+  float* scratch;              // swapped form with k_splits > 1: partial tiles [tile][split][BN][128]
 };
 
 constexpr int stage_bytes(int bn) { return (BM + bn) * BK * 2; }
@@ -219,8 +217,6 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   const uint32_t tmem_slot = acc_bar + 8;
   volatile uint32_t* tmem_slot_ptr =
       (volatile uint32_t*)(smem_raw + (tmem_slot - raw));
-  __shared__ int s_last;
-
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   sb_pdl_launch();
   // consecutive blocks walk the A tiles of one B tile (or K splits first, in the swapped form),
@@ -373,42 +369,6 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
 
-  if (SWAPPED && p.k_splits > 1) {
-    sb_pdl_wait();
-    // The block that arrives last at this tile's counter adds the partial tiles in split order
-    // and runs the epilogue; the counter is left at zero for the next launch.
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      const int seen = atomicAdd(&p.counters[tile_a], 1);
-      s_last = seen == p.k_splits - 1;
-      if (s_last) p.counters[tile_a] = 0;
-    }
-    __syncthreads();
-    if (!s_last) return;
-    __threadfence();
-    const float* base = p.scratch + (size_t)tile_a * p.k_splits * BN * BM;
-    for (int e = threadIdx.x; e < BM * BN; e += THREADS) {
-      const int f = e % BM, j = e / BM;                      // feature within the tile, token
-      if (j >= p.M) break;
-      const int n = tile_a * BM + f;
-      float v = 0.0f;
-      for (int s = 0; s < p.k_splits; ++s) v += base[((size_t)s * BN + j) * BM + f];
-      if (p.epilogue == SB_EPI_SWIGLU) {
-        if ((f & 15) >= 8 || n >= p.N) continue;
-        float up = 0.0f;
-        for (int s = 0; s < p.k_splits; ++s) up += base[((size_t)s * BN + j) * BM + f + 8];
-        ((TO*)p.out)[(size_t)j * (p.N / 2) + (n >> 4) * 8 + (n & 7)] = sb_from_f32<TO>(sb_silu(v) * up);
-        continue;
-      }
-      if (n >= p.N) continue;
-      if (p.epilogue == SB_EPI_BIAS)
-        v += p.bias_dtype == SB_F32 ? bias_at<float>(p.bias, n) : bias_at<bf16>(p.bias, n);
-      else if (p.epilogue == SB_EPI_RESIDUAL)
-        v += p.residual[(size_t)j * p.N + n];
-      ((TO*)p.out)[(size_t)j * p.N + n] = sb_from_f32<TO>(v);
-    }
-  }
 }
 
 // ------------------------------------------------------------------ the persistent kernel
@@ -543,6 +503,46 @@ gemm_tc5_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
   if (warp == 1) tmem_dealloc(tmem_base, 512);
 }
 
+// Adds the partial tiles of a split-K swapped product in split order and applies the epilogue.
+// One thread takes four consecutive features of one token (for the fused gate/up: four gates and
+// their four up values).  A second, fully parallel kernel measured faster here than letting the
+// block that finishes a tile last add its partials.
+template <typename TO>
+__global__ void __launch_bounds__(256)
+tc5_reduce_kernel(const Tc5Params p, int bn) {
+  sb_pdl_launch();
+  sb_pdl_wait();
+  const int n_out = p.epilogue == SB_EPI_SWIGLU ? p.N / 2 : p.N;
+  const int groups = (n_out + 3) / 4;
+  const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long)groups * p.M) return;
+  const int j = (int)(idx / groups), o0 = (int)(idx % groups) * 4;      // token, first output
+  float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f}, up[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+  // first feature of the group in W's row order
+  const int n0 = p.epilogue == SB_EPI_SWIGLU ? (o0 / 8) * 16 + (o0 % 8) : o0;
+  const int tile = n0 / BM, f = n0 % BM;
+  const float* base = p.scratch + (((size_t)tile * p.k_splits) * bn + j) * BM + f;
+  for (int s = 0; s < p.k_splits; ++s) {
+    const float4 v = *reinterpret_cast<const float4*>(base + (size_t)s * bn * BM);
+    acc[0] += v.x; acc[1] += v.y; acc[2] += v.z; acc[3] += v.w;
+    if (p.epilogue == SB_EPI_SWIGLU) {
+      const float4 u = *reinterpret_cast<const float4*>(base + (size_t)s * bn * BM + 8);
+      up[0] += u.x; up[1] += u.y; up[2] += u.z; up[3] += u.w;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int o = o0 + i;
+    if (o >= n_out) break;
+    float v = acc[i];
+    if (p.epilogue == SB_EPI_SWIGLU) v = sb_silu(v) * up[i];
+    else if (p.epilogue == SB_EPI_BIAS)
+      v += p.bias_dtype == SB_F32 ? bias_at<float>(p.bias, o) : bias_at<bf16>(p.bias, o);
+    else if (p.epilogue == SB_EPI_RESIDUAL) v += p.residual[(size_t)j * p.N + o];
+    ((TO*)p.out)[(size_t)j * n_out + o] = sb_from_f32<TO>(v);
+  }
+}
+
 // --------------------------------------------------------------------------- host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
@@ -639,11 +639,11 @@ namespace {
 
 int swapped_bn(int M) { return M <= 16 ? 16 : (M <= 32 ? 32 : 64); }
 
-// How many blocks share one output tile of the swapped form: enough to give every SM a block,
-// at least four K tiles each, and no block without work.
+// How many blocks share one output tile of the swapped form: enough to give every SM two
+// blocks, at least four K tiles each, and no block without work.
 int choose_splits(int N, int K, int n_sms) {
   const int tiles = (N + BM - 1) / BM, n_k = (K + BK - 1) / BK;
-  int splits = n_sms > 0 ? n_sms / tiles : 1;
+  int splits = n_sms > 0 ? 2 * n_sms / tiles : 1;       // two blocks fit an SM
   if (splits > 16) splits = 16;
   if (splits > n_k / 4) splits = n_k / 4;
   if (splits < 1) splits = 1;
@@ -651,25 +651,21 @@ int choose_splits(int N, int K, int n_sms) {
   return (n_k + k_per - 1) / k_per;
 }
 
-size_t counter_bytes(int tiles) { return ((size_t)tiles * sizeof(int) + 255) & ~(size_t)255; }
-
 }  // namespace
 
-// Bytes of scratch (tile counters + partial tiles) the swapped form needs for these sizes; 0
-// when K is not split.  The first counter_bytes must be zero before the first launch; the
-// kernel leaves them zero.
+// Bytes of scratch (partial tiles) the swapped form needs for these sizes; 0 when K is not split.
 extern "C" size_t sb_gemm_tc5_scratch_bytes(int M, int N, int K, int n_sms) {
   if (M > 64 || M <= 0 || N <= 0 || K <= 0) return 0;
   const int splits = choose_splits(N, K, n_sms);
   if (splits <= 1) return 0;
   const int tiles = (N + BM - 1) / BM;
-  return counter_bytes(tiles) + (size_t)tiles * splits * swapped_bn(M) * BM * sizeof(float);
+  return (size_t)tiles * splits * swapped_bn(M) * BM * sizeof(float);
 }
 
 extern "C" int sb_gemm_tc5(const void* A, int a_dtype, const void* W, int w_dtype, int M, int N,
                            int K, int epilogue, const void* bias, int bias_dtype,
                            const float* residual, void* out, int out_dtype, void* scratch,
-                           size_t scratch_bytes, int n_sms, cudaStream_t stream) {
+                           size_t scratch_bytes, int n_sms, int form, cudaStream_t stream) {
   if (int rc = sb_check_linear_args("sb_gemm_tc5", M, N, K, epilogue, bias, residual, out_dtype))
     return rc;
   if (a_dtype != SB_BF16 || w_dtype != SB_BF16)
@@ -683,9 +679,12 @@ extern "C" int sb_gemm_tc5(const void* A, int a_dtype, const void* W, int w_dtyp
 
   Tc5Params p;
   p.M = M; p.N = N; p.K = K; p.epilogue = epilogue; p.bias = bias; p.bias_dtype = bias_dtype;
-  p.residual = residual; p.out = out; p.k_splits = 1; p.scratch = nullptr; p.counters = nullptr;
+  p.residual = residual; p.out = out; p.k_splits = 1; p.scratch = nullptr;
   CUtensorMap ma, mb;
-  if (M > 64 && N >= 224 && n_sms > 0) {
+  // form: 0 picks by the number of rows, 1 forces the normal form, 2 the swapped form
+  const bool normal = form == 1 || (form == 0 && M > 64);
+  if (form == 2 && M > 64) SB_FAIL(SB_ERR_UNSUPPORTED, "sb_gemm_tc5: the swapped form takes at most 64 rows");
+  if (normal && N >= 224 && n_sms > 0) {
     // many rows, wide output: the persistent kernel
     const int bn = persistent_bn(M, N, n_sms);
     p.tiles_a = (M + BM - 1) / BM;
@@ -702,7 +701,7 @@ extern "C" int sb_gemm_tc5(const void* A, int a_dtype, const void* W, int w_dtyp
     if (out_dtype == SB_F32) return launch_persistent<224, 4, float>(ma, mb, p, blocks, stream);
     return launch_persistent<224, 4, bf16>(ma, mb, p, blocks, stream);
   }
-  if (M > 64) {
+  if (normal) {
     constexpr int BN = 128;
     p.tiles_a = (M + BM - 1) / BM;
     p.tiles_b = (N + BN - 1) / BN;
@@ -724,17 +723,26 @@ extern "C" int sb_gemm_tc5(const void* A, int a_dtype, const void* W, int w_dtyp
     if (!scratch || scratch_bytes < need)
       SB_FAIL(SB_ERR_ARG, "sb_gemm_tc5: %zu bytes of scratch needed, %zu given", need, scratch_bytes);
     if ((uintptr_t)scratch & 255) SB_FAIL(SB_ERR_ARG, "sb_gemm_tc5: scratch must be 256-byte aligned");
-    p.counters = (int*)scratch;                      // kept at zero by the kernel itself
-    p.scratch = (float*)((char*)scratch + counter_bytes(p.tiles_a));
+    p.scratch = (float*)scratch;
   }
   if (!make_map(&ma, W, N, K, BM) || !make_map(&mb, A, M, K, bn))
     SB_FAIL(SB_ERR_CUDA, "sb_gemm_tc5: cuTensorMapEncodeTiled failed");
   const int blocks = p.tiles_a * splits;
-#define SB_TC5_SWAPPED(BN_)                                                                  \
-  if (out_dtype == SB_F32) return launch<BN_, 6, true, float>(ma, mb, p, blocks, stream);     \
-  return launch<BN_, 6, true, bf16>(ma, mb, p, blocks, stream);
-  if (bn == 16) { SB_TC5_SWAPPED(16) }
-  if (bn == 32) { SB_TC5_SWAPPED(32) }
-  SB_TC5_SWAPPED(64)
+  int rc;
+  // stages are chosen so that two blocks fit an SM (about 100 KB of shared memory each)
+#define SB_TC5_SWAPPED(BN_, ST_)                                                             \
+  rc = out_dtype == SB_F32 ? launch<BN_, ST_, true, float>(ma, mb, p, blocks, stream)         \
+                           : launch<BN_, ST_, true, bf16>(ma, mb, p, blocks, stream);
+  if (bn == 16) { SB_TC5_SWAPPED(16, 6) }
+  else if (bn == 32) { SB_TC5_SWAPPED(32, 5) }
+  else { SB_TC5_SWAPPED(64, 4) }
 #undef SB_TC5_SWAPPED
+  if (rc != SB_OK || splits <= 1) return rc;
+  const int n_out = epilogue == SB_EPI_SWIGLU ? N / 2 : N;
+  const long work = (long)((n_out + 3) / 4) * M;
+  const dim3 rgrid((unsigned)((work + 255) / 256));
+  if (out_dtype == SB_F32) sb_launch(tc5_reduce_kernel<float>, rgrid, dim3(256), 0, stream, p, bn);
+  else sb_launch(tc5_reduce_kernel<bf16>, rgrid, dim3(256), 0, stream, p, bn);
+  SB_CHECK_LAUNCH("sb_gemm_tc5 (reduce)");
+  return SB_OK;
 }

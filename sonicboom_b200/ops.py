@@ -111,9 +111,12 @@ def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = 
            kernel: str = "auto") -> torch.Tensor:
     """out = a @ w.T with a fused epilogue; a [M,K], w [N,K]; float32 accumulation.
 
-    bfloat16 operands run on tensor cores (weight-streaming kernel up to SKINNY_MAX_ROWS rows,
-    tiled kernel above); float32 operands run on the plain FFMA kernel, which is also what
-    `kernel="plain"` forces for any dtypes.  Mixed operand dtypes are cast to float32 first.
+    bfloat16 operands run on tensor cores: `kernel` "tc5" (TMA + tcgen05), "skinny" (weights
+    streamed into mma.sync fragments, at most SKINNY_MAX_ROWS rows), "tiled" (mma.sync tiles),
+    or "auto", which picks between the first two (see `_pick_kernel`).  float32 operands, inner
+    sizes that are not multiples of 8, and `kernel="plain"` run the plain FFMA kernel.  A
+    bfloat16 activation with a float32 weight is cast to float32 first.  The split-K decode
+    form keeps one workspace per device, so products on one device must be ordered in a stream.
     """
     M, K = a.shape
     N = w.shape[0]
@@ -135,10 +138,11 @@ def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = 
     l = lib()
     if kernel == "auto" and fast:
         kernel = _pick_kernel(M, N, K, a.device)
-    if fast and kernel == "tc5":
-        ws = _tc5_workspace(M, N, K, a.device)
+    if fast and kernel in ("tc5", "tc5_normal"):
+        form = 1 if kernel == "tc5_normal" else 0
+        ws = _tc5_workspace(M, N, K, a.device) if form == 0 else None
         _check(l.sb_gemm_tc5(*args[:-1], _ptr(ws), ctypes.c_size_t(ws.numel() if ws is not None else 0),
-                             _sm_count(a.device), _stream()), "linear (tcgen05 kernel)")
+                             _sm_count(a.device), form, _stream()), "linear (tcgen05 kernel)")
     elif fast and kernel == "skinny":
         _check(l.sb_gemm_skinny(*args), "linear (weight-streaming kernel)")
     elif fast and kernel == "tiled":
@@ -154,23 +158,23 @@ FORCE_DECODE_KERNEL = None      # "skinny" or "tc5": overrides the choice below 
 
 
 def _pick_kernel(M: int, N: int, K: int, device) -> str:
-    """Which bfloat16 product kernel "auto" means.  Above SKINNY_MAX_ROWS rows: the tcgen05
-    kernel.  Up to that many rows the product is bound by reading W once: the tcgen05 kernel
-    in its swapped form when W gives every SM a tile (or K is long and the rows are few),
-    else the kernel that streams W into mma.sync fragments, whose fixed costs are lower on
-    small matrices (measured on B200 at the 7B layer sizes)."""
-    if M > SKINNY_MAX_ROWS:
+    """Which bfloat16 product kernel "auto" means.  The tcgen05 kernel, except for small
+    matrices at up to 16 rows: there the kernel that streams W into mma.sync fragments has lower
+    fixed costs (measured on B200 at the 7B layer sizes, inside CUDA graphs: 9 us against 12 us
+    for the 4608 x 3584 and 3584 x 3584 products at 8 rows, equal at 16 rows, while at 64 rows
+    the tcgen05 kernel takes 12 us and the streaming kernel 19 us)."""
+    if M > 16:
         return "tc5"
     if FORCE_DECODE_KERNEL:
         return FORCE_DECODE_KERNEL
     tiles = (N + 127) // 128
-    if tiles >= _sm_count(device) or (K >= 8192 and M <= 32):
+    if tiles >= _sm_count(device) or K >= 8192:
         return "tc5"
     return "skinny"
 
 
 _sm_counts: dict = {}
-_tc5_buffers: dict = {}          # device -> list of zero-initialised workspaces (never freed:
+_tc5_buffers: dict = {}          # device -> list of workspaces (never freed:
                                  # captured graphs may hold their addresses)
 
 
@@ -182,8 +186,8 @@ def _sm_count(device) -> int:
 
 
 def _tc5_workspace(M: int, N: int, K: int, device):
-    """Workspace of the split-K decode product: tile counters (zero between launches) and
-    partial tiles.  One buffer per device serves every call on the stream; it only grows."""
+    """Workspace of the split-K decode product: the partial tiles.  One buffer per device
+    serves every call on the stream; it only grows."""
     l = lib()
     l.sb_gemm_tc5_scratch_bytes.restype = ctypes.c_size_t
     need = int(l.sb_gemm_tc5_scratch_bytes(M, N, K, _sm_count(device)))
@@ -192,7 +196,7 @@ def _tc5_workspace(M: int, N: int, K: int, device):
     key = torch.device(device).index or 0
     bufs = _tc5_buffers.setdefault(key, [])
     if not bufs or bufs[-1].numel() < need:
-        bufs.append(torch.zeros(max(need, 8 << 20), dtype=torch.uint8, device=device))
+        bufs.append(torch.empty(max(need, 16 << 20), dtype=torch.uint8, device=device))
     return bufs[-1]
 
 
