@@ -77,9 +77,12 @@ __device__ __forceinline__ void sb_pdl_launch() {
   asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
 }
 
-extern "C" int sb_pdl_enabled();      // per library; set with sb_set_pdl
+extern "C" int sb_pdl_enabled();      // per library: 0 off, 1 every kernel, 2 only kernels that
+                                      // prefetch weights before their wait; set with sb_set_pdl
 
-template <typename... Exp, typename... Act>
+// `prefetches`: the kernel requests weights before its dependency wait (it gains from an early
+// start even when its neighbours do not).
+template <bool prefetches = false, typename... Exp, typename... Act>
 inline cudaError_t sb_launch(void (*kernel)(Exp...), dim3 grid, dim3 block, size_t smem,
                              cudaStream_t stream, Act&&... args) {
   cudaLaunchConfig_t cfg = {};
@@ -91,7 +94,8 @@ inline cudaError_t sb_launch(void (*kernel)(Exp...), dim3 grid, dim3 block, size
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = sb_pdl_enabled() ? 1 : 0;
+  const int level = sb_pdl_enabled();
+  cfg.numAttrs = (level == 1 || (level == 2 && prefetches)) ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<Exp>(args)...);
 }
 

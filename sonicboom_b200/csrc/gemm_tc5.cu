@@ -586,8 +586,8 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const Tc5Params& p, int
       SB_FAIL(SB_ERR_CUDA, "sb_gemm_tc5: shared memory opt-in failed: %s", cudaGetErrorString(e));
     configured = true;
   }
-  sb_launch(gemm_tc5_kernel<BN, STAGES, SWAPPED, TO>, dim3(blocks), dim3(THREADS), smem, stream, ma,
-            mb, p);
+  sb_launch<true>(gemm_tc5_kernel<BN, STAGES, SWAPPED, TO>, dim3(blocks), dim3(THREADS), smem, stream,
+                  ma, mb, p);
   SB_CHECK_LAUNCH("sb_gemm_tc5");
   return SB_OK;
 }

@@ -142,7 +142,8 @@ def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = 
         form = 1 if kernel == "tc5_normal" else 0
         ws = _tc5_workspace(M, N, K, a.device) if form == 0 else None
         _check(l.sb_gemm_tc5(*args[:-1], _ptr(ws), ctypes.c_size_t(ws.numel() if ws is not None else 0),
-                             _sm_count(a.device), form, _stream()), "linear (tcgen05 kernel)")
+                             _sm_count(a.device), form, _stream()), "linear (tcgen05 kernel)",
+               launches=2 if ws is not None else 1)        # a split product adds its reduce kernel
     elif fast and kernel == "skinny":
         _check(l.sb_gemm_skinny(*args), "linear (weight-streaming kernel)")
     elif fast and kernel == "tiled":
@@ -200,13 +201,14 @@ def _tc5_workspace(M: int, N: int, K: int, device):
     return bufs[-1]
 
 
-def set_pdl(on: bool) -> None:
-    """Turns programmatic dependent launch of the kernels on or off (off by default; the
-    environment variable SB_PDL=1 turns it on at start)."""
-    lib().sb_set_pdl(1 if on else 0)
+def set_pdl(level) -> None:
+    """Programmatic dependent launch of the kernels: 0 (or False) off, 1 (or True) every
+    kernel, 2 only the tcgen05 products.  The environment variable SB_PDL sets it at start."""
+    level = int(level)
+    lib().sb_set_pdl(level)
     for l in _attn_libs.values():
         if l is not None:
-            l.sb_set_pdl(1 if on else 0)
+            l.sb_set_pdl(level)
 
 
 def tc5_status() -> int:
