@@ -203,6 +203,15 @@ __device__ __forceinline__ void load_q_frags(uint32_t qs, int warp_row0, int lan
   }
 }
 
+}  // namespace
+
+#if SB_HD == 64 || SB_HD == 128
+#define SB_ATTN_TC5 1
+#include "attn_tc5.cuh"
+#endif
+
+namespace {
+
 // ------------------------------------------------------------------------------- prefill
 constexpr int PREFILL_SMEM = (BM + 4 * KT) * LDS * 2;
 
@@ -491,6 +500,21 @@ int n_splits_for(int max_len) { return (max_len + SPLIT_PAGES * KT - 1) / (SPLIT
 
 extern "C" int sb_attention_head_dim() { return HD; }
 
+// Prefill kernel choice: 0 (default) the tensor-memory kernel where it applies, 1 always the
+// mma.sync kernel (tests compare the two).
+static int g_force_mma = 0;
+extern "C" void sb_attention_force_mma(int on) { g_force_mma = on; }
+
+// 0 when no tensor-memory kernel of this library has given up on a wait since the last call,
+// else the code of that wait; -1 when this head size has no such kernel.
+extern "C" int sb_attention_status() {
+#ifdef SB_ATTN_TC5
+  return tc5_read_status();
+#else
+  return -1;
+#endif
+}
+
 // Bytes of scratch sb_attention needs for a step with these bounds (0 when none is used).
 extern "C" size_t sb_attention_scratch_bytes(int n_rows, int n_q_heads, int n_kv_heads, int max_new,
                                              int max_len) {
@@ -511,7 +535,8 @@ extern "C" int sb_attention(const void* q, void* out, int n_rows, int n_seqs, in
                             const int32_t* page_off, const int32_t* page_ids, int page_size,
                             const void* cache, int n_q_heads, int n_kv_heads, int hd, int window,
                             float scale, void* scratch, size_t scratch_bytes, int* counters,
-                            int n_counters, int max_len, int n_sms, cudaStream_t stream) {
+                            int n_counters, int max_len, int n_pages, int n_sms,
+                            cudaStream_t stream) {
   if (hd != HD) SB_FAIL(SB_ERR_ARG, "sb_attention: built for head size %d, called with %d", HD, hd);
   if (page_size != KT)
     SB_FAIL(SB_ERR_UNSUPPORTED, "sb_attention: cache pages of %d keys (needs %d)", page_size, KT);
@@ -557,6 +582,44 @@ extern "C" int sb_attention(const void* q, void* out, int n_rows, int n_seqs, in
     return SB_OK;
   }
   p.n_splits = 1;
+#ifdef SB_ATTN_TC5
+  // tensor-memory kernel: needs the extent of the cache entry for its tensor map, row
+  // coordinates that fit an int, and a positive scale (it takes the maximum before scaling)
+  const long cache_rows = (long)n_pages * 2 * n_kv_heads * KT;
+  static bool tc5_checked = false, tc5_misaligned = false;
+  if (n_pages > 0 && cache_rows < 2147483647L && scale > 0.0f && !g_force_mma && !tc5_misaligned) {
+    static bool configured5 = false;
+    if (!configured5) {
+      cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc5_kernel,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, T5_SMEM);
+      if (e != cudaSuccess)
+        SB_FAIL(SB_ERR_CUDA, "sb_attention: shared memory opt-in failed: %s", cudaGetErrorString(e));
+      configured5 = true;
+    }
+    CUtensorMap map_kv;
+    if (!t5_make_map(&map_kv, cache, cache_rows))
+      SB_FAIL(SB_ERR_CUDA, "sb_attention: cuTensorMapEncodeTiled failed");
+    const long tiles5 = ((long)max_new * G + T5_QT * T5_ROWS - 1) / (T5_QT * T5_ROWS);
+    if (tiles5 > 2147483647L) SB_FAIL(SB_ERR_UNSUPPORTED, "sb_attention: too many rows");
+    sb_launch(attn_prefill_tc5_kernel, dim3((unsigned)tiles5, n_kv_heads, n_seqs),
+              dim3(T5_THREADS), T5_SMEM, stream, map_kv, p);
+    SB_CHECK_LAUNCH("sb_attention (prefill, tcgen05)");
+    if (tc5_checked) return SB_OK;
+    // Once: the kernel's tiles need shared memory that starts on a 1024-byte boundary, which it
+    // checks itself (status 10, nothing computed).  Should that ever be reported, this step and
+    // all later ones run on the mma.sync kernel.
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone)
+      return SB_OK;
+    if (cudaStreamSynchronize(stream) != cudaSuccess)
+      SB_FAIL(SB_ERR_CUDA, "sb_attention: the tensor-memory prefill kernel failed");
+    tc5_checked = true;
+    const int st = tc5_read_status();
+    if (st == 0) return SB_OK;
+    if (st != 10) SB_FAIL(SB_ERR_CUDA, "sb_attention: a wait in the tensor-memory kernel gave up (code %d)", st);
+    tc5_misaligned = true;
+  }
+#endif
   const long tiles = ((long)max_new * G + BM - 1) / BM;
   if (tiles > 2147483647L) SB_FAIL(SB_ERR_UNSUPPORTED, "sb_attention: too many rows");
   sb_launch(attn_prefill_kernel, dim3((unsigned)tiles, n_kv_heads, n_seqs), dim3(PREFILL_THREADS), PREFILL_SMEM,

@@ -17,9 +17,7 @@
 //
 // Every wait on an mbarrier is bounded; when a bound is hit the kernel records a code in a
 // status word, stops issuing work and leaves normally (sb_tc5_status reads the word).
-#include <cuda.h>
-
-#include "common.cuh"
+#include "tc5.cuh"
 
 int sb_check_linear_args(const char* who, int M, int N, int K, int epilogue, const void* bias,
                          const float* residual, int out_dtype);
@@ -30,97 +28,6 @@ typedef __nv_bfloat16 bf16;
 
 constexpr int BM = 128, BK = 64, UMMA_K = 16;
 constexpr int THREADS = 192;
-constexpr uint32_t WAIT_LIMIT = 1u << 22;
-
-__device__ int g_status = 0;          // 0 ok; else the code of the wait that gave up
-
-// ------------------------------------------------------------------------- PTX wrappers
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes)
-               : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n.reg .pred p;\n"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-      "selp.u32 %0, 1, 0, p;\n}\n"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Bounded wait: false (and a status code) when the barrier did not flip in time.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int code) {
-  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if (i > 4096) __nanosleep(128);
-  }
-  atomicCAS(&g_status, 0, code);
-  return false;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y,
-                                            uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, "
-      "{%2, %3}], [%4];\n" ::"r"(dst),
-      "l"(map), "r"(x), "r"(y), "r"(bar)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(dst_smem),
-               "r"(cols));
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(taddr), "r"(cols));
-}
-__device__ __forceinline__ void tc_fence_before() {
-  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-}
-__device__ __forceinline__ void tc_fence_after() {
-  asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-}
-__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
-                                          uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n.reg .pred p;\n"
-      "setp.ne.b32 p, %4, 0;\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem),
-      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar)
-               : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
-        "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]),
-        "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]),
-        "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-}
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
-        "=r"(r[15])
-      : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-}
-
 // Shared-memory matrix descriptor of a K-major tile with the 128-byte swizzle: rows of 128
 // bytes, groups of 8 rows 1024 bytes apart.
 __device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
@@ -377,10 +284,6 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 // tiles through L2).  Tiles are 128 x BN with BN up to 256, which halves the operand traffic per
 // flop of the 128 x 128 kernel; tensor memory holds two accumulators, so the epilogue of a tile
 // runs while the MMAs of the block's next tile are already being issued.
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
-}
-
 constexpr int PERSIST_STAGING = 4 * 32 * 33 * 4;     // the epilogue warps' transpose tiles
 constexpr int persist_smem_bytes(int bn, int stages) {
   return stages * stage_bytes(bn) + PERSIST_STAGING + 1024 + 256;
@@ -544,23 +447,6 @@ tc5_reduce_kernel(const Tc5Params p, int bn) {
 }
 
 // --------------------------------------------------------------------------- host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
-                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
-                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = (EncodeTiledFn)ptr;
-  }
-  return fn;
-}
-
 // A [rows, K] bfloat16 row-major matrix as a tensor map with boxes of box_rows x 64.
 bool make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) {
   EncodeTiledFn fn = encode_fn();
@@ -628,12 +514,7 @@ int persistent_bn(int M, int N, int n_sms) {
 // 0 when no kernel has given up on a wait since the last call; else the code of the wait
 // (1 producer/empty, 2 producer drain, 3 MMA/full, 4 epilogue/accumulator).  Reading
 // synchronizes with the device.
-extern "C" int sb_tc5_status() {
-  int v = -1, zero = 0;
-  if (cudaMemcpyFromSymbol(&v, g_status, sizeof(int)) != cudaSuccess) return -1;
-  if (v != 0) cudaMemcpyToSymbol(g_status, &zero, sizeof(int));
-  return v;
-}
+extern "C" int sb_tc5_status() { return tc5_read_status(); }
 
 namespace {
 

@@ -270,7 +270,8 @@ def attention(q: torch.Tensor, out: torch.Tensor, plan, group_index: int, cache:
     """Causal grouped-query attention of the step's rows over one cache entry's pages.
 
     bfloat16 runs the tensor-core kernels (built for the head size at first use); float32, a
-    head size those kernels do not take, or `kernel="plain"` run the plain kernel."""
+    head size those kernels do not take, or `kernel="plain"` run the plain kernel.  `"mma"` keeps
+    prefill on the mma.sync kernel where the tensor-memory kernel would run (head sizes 64, 128)."""
     n = q.shape[0]
     g = plan.groups[group_index]
     al = attention_lib(head_dim) if (q.dtype == torch.bfloat16 and cache.dtype == torch.bfloat16
@@ -279,13 +280,18 @@ def attention(q: torch.Tensor, out: torch.Tensor, plan, group_index: int, cache:
         need = int(al.sb_attention_scratch_bytes(n, n_q_heads, n_kv_heads, plan.max_new, plan.max_len))
         scratch = plan.scratch(need, q.device)
         counters = _attn_counters(plan.n_seqs * n_kv_heads, q.device)
+        if kernel == "mma":
+            al.sb_attention_force_mma(1)
         rc = al.sb_attention(
             _ptr(q), _ptr(out), n, plan.n_seqs, plan.max_new, _i32(plan.seq_row0, "seq_row0"),
             _i32(plan.seq_pos0, "seq_pos0"), _i32(g.page_off, "page_off"),
             _i32(g.page_ids, "page_ids"), g.page_size, _ptr(cache), n_q_heads, n_kv_heads,
             head_dim, window, ctypes.c_float(scale), _ptr(scratch),
             ctypes.c_size_t(scratch.numel() if scratch is not None else 0),
-            _ptr(counters), counters.numel(), plan.max_len, _sm_count(q.device), _stream())
+            _ptr(counters), counters.numel(), plan.max_len, cache.shape[0], _sm_count(q.device),
+            _stream())
+        if kernel == "mma":
+            al.sb_attention_force_mma(0)
         if rc != 0:
             raise KernelError(f"attention: {al.sb_last_error().decode()}")
         global LAUNCHES
@@ -298,6 +304,13 @@ def attention(q: torch.Tensor, out: torch.Tensor, plan, group_index: int, cache:
             n_q_heads, n_kv_heads, head_dim, window, ctypes.c_float(scale), _stream()),
             "attention (plain kernel)")
     return out
+
+
+def attention_status(head_dim: int) -> int:
+    """0 when no tensor-memory attention kernel of this head size has given up on a wait since the
+    last call (else the code of that wait); -1 when the head size has no such kernel."""
+    al = attention_lib(head_dim)
+    return int(al.sb_attention_status()) if al is not None else -1
 
 
 def sample_params_size() -> int:

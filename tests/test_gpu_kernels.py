@@ -192,10 +192,12 @@ def attention_ref(qkv, pos0, hq, hkv, hd, window, history=None, theta=10000.0, s
 @pytest.mark.parametrize("hq,hkv,hd", [(4, 2, 16), (6, 1, 32), (5, 5, 48), (14, 2, 64), (28, 4, 128),
                                        (3, 1, 80), (8, 8, 256)])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("kernel", ["plain", "auto"])
+@pytest.mark.parametrize("kernel", ["plain", "auto", "mma"])
 def test_rotation_cache_and_attention(hq, hkv, hd, dtype, kernel):
-    if dtype == "float32" and kernel == "auto":
+    if dtype == "float32" and kernel != "plain":
         pytest.skip("float32 has the plain kernel only")
+    if kernel == "mma" and hd not in (64, 128):
+        pytest.skip("auto already is the mma.sync kernel at this head size")
     tol = 1e-5 if dtype == "float32" else 1.5e-2
     for window in (0, 37):
         cache = make_cache(hkv, hd, window, DT[dtype])
@@ -319,6 +321,47 @@ def test_every_sequence_reads_its_own_pages(dtype, kernel):
         assert abs(float(out[i].mean()) - want) < 0.01 * want + 0.5, (i, float(out[i].mean()), want)
     pages = [cache.page_list(s, 0) for s in slots]
     assert pages[0][1] != pages[0][0] + 1                 # the pool really was interleaved
+
+
+@pytest.mark.parametrize("hq,hkv,hd,window,lens", [
+    (28, 4, 128, 0, [700, 37]), (28, 4, 128, 100, [700, 333]), (8, 8, 128, 0, [513]),
+    (7, 1, 64, 0, [1000]), (14, 2, 64, 37, [300, 5]), (6, 2, 64, 200, [450])])
+def test_long_prefill_on_the_tensor_memory_kernel(hq, hkv, hd, window, lens):
+    """Prompts of many pages, several query tiles per block, windows that start inside a page:
+    the tcgen05 prefill kernel against the plain implementation; no wait in it may give up."""
+    cache = make_cache(hkv, hd, window, torch.bfloat16, max_tokens=sum((n + 63) // 64 * 64 for n in lens))
+    xs = [torch.randn(n, (hq + 2 * hkv) * hd, generator=torch.Generator().manual_seed(n)) for n in lens]
+    slots = [cache.open() for _ in lens]
+    out, _ = run_attention(cache, hq, hkv, hd, window, torch.bfloat16, list(zip(slots, xs)))
+    at = 0
+    for x in xs:
+        close(out[at:at + x.shape[0]], attention_ref(x, 0, hq, hkv, hd, window), 1.5e-2)
+        at += x.shape[0]
+    assert ops.attention_status(hd) == 0
+
+
+def test_prefill_continues_a_sequence_on_the_tensor_memory_kernel():
+    """A second prompt chunk (positions do not start at 0) sees the first chunk's keys."""
+    hq, hkv, hd = 14, 2, 128
+    cache = make_cache(hkv, hd, 0, torch.bfloat16)
+    s = cache.open()
+    x = torch.randn(500, (hq + 2 * hkv) * hd, generator=torch.Generator().manual_seed(3))
+    run_attention(cache, hq, hkv, hd, 0, torch.bfloat16, [(s, x[:230])])
+    out, _ = run_attention(cache, hq, hkv, hd, 0, torch.bfloat16, [(s, x[230:])])
+    close(out, attention_ref(x[230:], 230, hq, hkv, hd, 0, history=x[:230]), 1.5e-2)
+    assert ops.attention_status(hd) == 0
+
+
+def test_a_far_key_is_found_by_the_tensor_memory_kernel():
+    hq, hkv, hd, n = 8, 2, 64, 900
+    for key_pos in (3, 64, 255, 511, 640, 895):
+        cache = make_cache(hkv, hd, 0, torch.bfloat16)
+        x = standout(n, hq, hkv, hd, key_pos)
+        out, _ = run_attention(cache, hq, hkv, hd, 0, torch.bfloat16, [(cache.open(), x)], rot=0)
+        last = out[-1]
+        assert abs(float(last.mean()) - (key_pos + 1)) < 0.02 * (key_pos + 1), (key_pos, float(last.mean()))
+        first = out[key_pos]                              # the row of the key itself sees it too
+        assert abs(float(first.mean()) - (key_pos + 1)) < 0.02 * (key_pos + 1)
 
 
 # --------------------------------------------------------------------------------- sampling
