@@ -295,10 +295,11 @@ __global__ void __launch_bounds__(PREFILL_THREADS) attn_prefill_kernel(const Att
 // Shared memory: Q [16][LDS] bf16, then two stages of K and V tiles [64][LDS]; after the keys
 // are done the tiles' space is reused for the warps' partial outputs.
 constexpr int DECODE_SMEM = (DEC_ROWS + 4 * KT) * LDS * 2;
-constexpr int PART_STRIDE = HD + 2;    // floats per partial row: o[HD], m, l
+constexpr int PART_STRIDE = HD + 4;    // floats per partial row: o[HD], m, l (rows stay 16-byte aligned)
 constexpr bool DECODE_FITS = DECODE_SMEM <= 227 * 1024;
 static_assert(DEC_WARPS * 16 == KT, "each warp takes 16 keys of a tile");
-static_assert(DEC_WARPS * DEC_ROWS * PART_STRIDE * 4 <= 4 * KT * LDS * 2, "partials fit the tiles");
+static_assert((DEC_WARPS * DEC_ROWS * PART_STRIDE + (DEC_WARPS + 2) * DEC_ROWS) * 4 <= 4 * KT * LDS * 2,
+              "partials and weights fit the tiles");
 
 __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(const AttnParams p) {
   extern __shared__ __align__(128) unsigned char smem[];
@@ -375,49 +376,67 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(const AttnP
     l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
   }
   float* part = reinterpret_cast<float*>(smem + DEC_ROWS * LDS * 2);   // [warp][16][PART_STRIDE]
+  float* fac = part + DEC_WARPS * DEC_ROWS * PART_STRIDE;              // [warp][16] weights
+  float* row_m = fac + DEC_WARPS * DEC_ROWS;                           // [16] merged maximum
+  float* row_l = row_m + DEC_ROWS;                                     // [16] merged sum
   const int t4 = lane & 3;
 #pragma unroll
   for (int half = 0; half < 2; ++half) {
     float* dst = part + ((size_t)warp * DEC_ROWS + (half ? rb : ra)) * PART_STRIDE;
 #pragma unroll
-    for (int j = 0; j < HD / 8; ++j) {
-      dst[j * 8 + 2 * t4] = o[j][half * 2];
-      dst[j * 8 + 2 * t4 + 1] = o[j][half * 2 + 1];
-    }
+    for (int j = 0; j < HD / 8; ++j)
+      *reinterpret_cast<float2*>(dst + j * 8 + 2 * t4) = make_float2(o[j][half * 2], o[j][half * 2 + 1]);
     if (t4 == 0) {
       dst[HD] = m[half];
       dst[HD + 1] = l[half];
     }
   }
   __syncthreads();
-  // merge the warps in warp order: a thread handles (row, d) pairs
-  const bool single = split_lo == split_hi;
-  for (int idx = tid; idx < R * HD; idx += DEC_WARPS * 32) {
-    const int row = idx / HD, d = idx % HD;
+  // merge the warps in warp order: first each row's weights exp2(m_w - max) and its sum,
+  if (tid < DEC_ROWS) {
     float mm = -INFINITY;
 #pragma unroll
     for (int w = 0; w < DEC_WARPS; ++w)
-      mm = fmaxf(mm, part[((size_t)w * DEC_ROWS + row) * PART_STRIDE + HD]);
+      mm = fmaxf(mm, part[((size_t)w * DEC_ROWS + tid) * PART_STRIDE + HD]);
     const float base = mm == -INFINITY ? 0.0f : mm;
-    float acc = 0.0f, ll = 0.0f;
+    float ll = 0.0f;
 #pragma unroll
     for (int w = 0; w < DEC_WARPS; ++w) {
-      const float* src = part + ((size_t)w * DEC_ROWS + row) * PART_STRIDE;
+      const float* src = part + ((size_t)w * DEC_ROWS + tid) * PART_STRIDE;
       const float f = exp2f(src[HD] - base);
-      acc += src[d] * f;
+      fac[w * DEC_ROWS + tid] = f;
       ll += src[HD + 1] * f;
     }
-    const int tok = row / G, g = row % G;
+    row_m[tid] = mm;
+    row_l[tid] = ll;
+  }
+  __syncthreads();
+  // then the outputs, four values of a row per thread
+  const bool single = split_lo == split_hi;
+  for (int item = tid; item < R * (HD / 4); item += DEC_WARPS * 32) {
+    const int row = item / (HD / 4), c = item % (HD / 4);
+    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+    for (int w = 0; w < DEC_WARPS; ++w) {
+      const float4 v = *reinterpret_cast<const float4*>(
+          part + ((size_t)w * DEC_ROWS + row) * PART_STRIDE + 4 * c);
+      const float f = fac[w * DEC_ROWS + row];
+      acc.x += v.x * f; acc.y += v.y * f; acc.z += v.z * f; acc.w += v.w * f;
+    }
+    const size_t out_row = (size_t)(row0 + row / G) * p.n_q_heads + kvh * G + row % G;
     if (single) {
-      p.out[((size_t)(row0 + tok) * p.n_q_heads + kvh * G + g) * HD + d] = __float2bfloat16_rn(acc / ll);
+      const float inv = 1.0f / row_l[row];
+      uint2 v;
+      v.x = pack_bf16(acc.x * inv, acc.y * inv);
+      v.y = pack_bf16(acc.z * inv, acc.w * inv);
+      *reinterpret_cast<uint2*>(p.out + out_row * HD + 4 * c) = v;
     } else {
-      // scratch: [row of the batch][query head][split][HD + 2]
-      float* dst = p.scratch +
-                   (((size_t)(row0 + tok) * p.n_q_heads + kvh * G + g) * p.n_splits + split) * PART_STRIDE;
-      dst[d] = acc;
-      if (d == 0) {
-        dst[HD] = mm;
-        dst[HD + 1] = ll;
+      // scratch: [row of the batch][query head][split][PART_STRIDE]
+      float* dst = p.scratch + (out_row * p.n_splits + split) * PART_STRIDE;
+      *reinterpret_cast<float4*>(dst + 4 * c) = acc;
+      if (c == 0) {
+        dst[HD] = row_m[row];
+        dst[HD + 1] = row_l[row];
       }
     }
   }
@@ -437,17 +456,19 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(const AttnP
   if (!s_last) return;
   __threadfence();
   // Final merge.  The splits' (m, l) go to shared memory first, one thread per row turns
-  // them into weights exp2(m_s - max) and the row's 1 / sum, and then every (row, d) is a
-  // weighted sum whose loads are independent of each other and issued eight at a time.
+  // them into weights exp2(m_s - max) and the row's 1 / sum, and then four values of a row
+  // are a weighted sum over the splits whose loads are independent of each other and issued
+  // eight at a time (partials come from other blocks: they are read from L2).
   const int ns = split_hi - split_lo + 1;
   float* wgt = part;                               // [row][ns]
   float* den = part + DEC_ROWS * ns;               // [row][ns], then den[row * ns] = 1 / sum
   for (int i = tid; i < R * ns; i += DEC_WARPS * 32) {
     const int row = i / ns, sp = split_lo + i % ns;
     const size_t out_row = (size_t)(row0 + row / G) * p.n_q_heads + kvh * G + row % G;
-    const float* src = p.scratch + (out_row * p.n_splits + sp) * PART_STRIDE;
-    wgt[i] = src[HD];
-    den[i] = src[HD + 1];
+    const float2 ml = __ldcg(reinterpret_cast<const float2*>(
+        p.scratch + (out_row * p.n_splits + sp) * PART_STRIDE + HD));
+    wgt[i] = ml.x;
+    den[i] = ml.y;
   }
   __syncthreads();
   if (tid < R) {
@@ -463,30 +484,42 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(const AttnP
     den[tid * ns] = 1.0f / sum;
   }
   __syncthreads();
-  for (int idx = tid; idx < R * HD; idx += DEC_WARPS * 32) {
-    const int row = idx / HD, d = idx % HD;
+  for (int item = tid; item < R * (HD / 4); item += DEC_WARPS * 32) {
+    const int row = item / (HD / 4), c = item % (HD / 4);
     const size_t out_row = (size_t)(row0 + row / G) * p.n_q_heads + kvh * G + row % G;
-    const float* src = p.scratch + (out_row * p.n_splits + split_lo) * PART_STRIDE + d;
+    const float* src = p.scratch + (out_row * p.n_splits + split_lo) * PART_STRIDE + 4 * c;
     const float* w = wgt + row * ns;
-    float acc = 0.0f;
+    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     int i = 0;
     for (; i + 8 <= ns; i += 8) {
-      float v[8];
+      float4 v[8];
 #pragma unroll
-      for (int u = 0; u < 8; ++u) v[u] = src[(size_t)(i + u) * PART_STRIDE];
+      for (int u = 0; u < 8; ++u)
+        v[u] = __ldcg(reinterpret_cast<const float4*>(src + (size_t)(i + u) * PART_STRIDE));
 #pragma unroll
-      for (int u = 0; u < 8; ++u) acc = fmaf(v[u], w[i + u], acc);
+      for (int u = 0; u < 8; ++u) {
+        acc.x = fmaf(v[u].x, w[i + u], acc.x); acc.y = fmaf(v[u].y, w[i + u], acc.y);
+        acc.z = fmaf(v[u].z, w[i + u], acc.z); acc.w = fmaf(v[u].w, w[i + u], acc.w);
+      }
     }
-    for (; i + 4 <= ns; i += 4) {
-      const float v0 = src[(size_t)i * PART_STRIDE], v1 = src[(size_t)(i + 1) * PART_STRIDE];
-      const float v2 = src[(size_t)(i + 2) * PART_STRIDE], v3 = src[(size_t)(i + 3) * PART_STRIDE];
-      acc = fmaf(v0, w[i], acc);
-      acc = fmaf(v1, w[i + 1], acc);
-      acc = fmaf(v2, w[i + 2], acc);
-      acc = fmaf(v3, w[i + 3], acc);
+    if (i < ns) {                                   // up to seven left: loaded together as well
+      float4 v[7];
+#pragma unroll
+      for (int u = 0; u < 7; ++u)
+        v[u] = i + u < ns ? __ldcg(reinterpret_cast<const float4*>(src + (size_t)(i + u) * PART_STRIDE))
+                          : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+      for (int u = 0; u < 7; ++u) {
+        if (i + u >= ns) break;
+        acc.x = fmaf(v[u].x, w[i + u], acc.x); acc.y = fmaf(v[u].y, w[i + u], acc.y);
+        acc.z = fmaf(v[u].z, w[i + u], acc.z); acc.w = fmaf(v[u].w, w[i + u], acc.w);
+      }
     }
-    for (; i < ns; ++i) acc = fmaf(src[(size_t)i * PART_STRIDE], w[i], acc);
-    p.out[out_row * HD + d] = __float2bfloat16_rn(acc * den[row * ns]);
+    const float inv = den[row * ns];
+    uint2 v;
+    v.x = pack_bf16(acc.x * inv, acc.y * inv);
+    v.y = pack_bf16(acc.z * inv, acc.w * inv);
+    *reinterpret_cast<uint2*>(p.out + out_row * HD + 4 * c) = v;
   }
 }
 
@@ -548,7 +581,8 @@ extern "C" int sb_attention(const void* q, void* out, int n_rows, int n_seqs, in
             n_q_heads, n_kv_heads);
   if (n_kv_heads > 65535 || n_seqs > 65535)
     SB_FAIL(SB_ERR_UNSUPPORTED, "sb_attention: %d key/value heads, %d sequences", n_kv_heads, n_seqs);
-  if (((uintptr_t)q | (uintptr_t)cache) & 15) SB_FAIL(SB_ERR_ARG, "sb_attention: unaligned operands");
+  if ((((uintptr_t)q | (uintptr_t)cache | (uintptr_t)scratch) & 15) || ((uintptr_t)out & 7))
+    SB_FAIL(SB_ERR_ARG, "sb_attention: unaligned operands");
   AttnParams p;
   p.q = (const bf16*)q; p.out = (bf16*)out;
   p.seq_row0 = seq_row0; p.seq_pos0 = seq_pos0; p.page_off = page_off; p.page_ids = page_ids;
@@ -666,7 +700,8 @@ extern "C" int sb_attention_decode_static(const void* q, void* out, int n_rows, 
             max_new, max_len, n_q_heads, n_kv_heads);
   if (n_kv_heads > 65535 || n_seqs > 65535 || n_q_heads > 65535)
     SB_FAIL(SB_ERR_UNSUPPORTED, "%s: %d/%d heads, %d sequences", who, n_q_heads, n_kv_heads, n_seqs);
-  if (((uintptr_t)q | (uintptr_t)cache) & 15) SB_FAIL(SB_ERR_ARG, "%s: unaligned operands", who);
+  if ((((uintptr_t)q | (uintptr_t)cache) & 15) || ((uintptr_t)out & 7))
+    SB_FAIL(SB_ERR_ARG, "%s: unaligned operands", who);
   const int G = n_q_heads / n_kv_heads;
   if (max_new * G > DEC_ROWS || !DECODE_FITS || n_splits_for(max_len) > MAX_MERGE_SPLITS)
     SB_FAIL(SB_ERR_UNSUPPORTED,

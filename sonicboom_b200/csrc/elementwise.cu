@@ -292,6 +292,75 @@ __global__ void rope_store_kernel(const float* qkv, int n_q_heads, int n_kv_head
   }
 }
 
+// The same work four values at a time, for bfloat16 outputs: a task is four pairs (e, e + half)
+// of one head, or four of the values beyond the rotated part.  float4 loads and 8-byte stores;
+// needs half and (hd - rot) to be multiples of 4.
+__device__ __forceinline__ void store_bf16x4(__nv_bfloat16* dst, float a, float b, float c, float d) {
+  __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+  uint2 v;
+  v.x = *reinterpret_cast<uint32_t*>(&lo);
+  v.y = *reinterpret_cast<uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(dst) = v;
+}
+
+__global__ void rope_store_vec_kernel(const float* qkv, int n_q_heads, int n_kv_heads, int hd,
+                                      int rot, const float* __restrict__ inv_freq,
+                                      const int32_t* row_seq, const int32_t* row_pos,
+                                      const int32_t* page_off, const int32_t* page_ids,
+                                      int page_size, __nv_bfloat16* cache, __nv_bfloat16* q_out,
+                                      int has_kv) {
+  extern __shared__ float cs[];                      // cos[rot/2], then sin[rot/2]
+  sb_pdl_launch();
+  sb_pdl_wait();
+  const int t = blockIdx.x;
+  const int pos = row_pos[t];
+  const int half = rot >> 1;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    const float theta = (float)pos * inv_freq[i];
+    cs[i] = cosf(theta);
+    cs[half + i] = sinf(theta);
+  }
+  __syncthreads();
+  const int n_heads = n_q_heads + (has_kv ? 2 * n_kv_heads : 0);
+  const float* src_row = qkv + (size_t)t * n_heads * hd;
+  size_t k_base = 0, v_base = 0;
+  if (has_kv) {
+    const int page = page_ids[page_off[row_seq[t]] + pos / page_size];
+    k_base = (((size_t)page * 2) * n_kv_heads * page_size + pos % page_size) * hd;
+    v_base = (((size_t)page * 2 + 1) * n_kv_heads * page_size + pos % page_size) * hd;
+  }
+  const int pair_tasks = half >> 2, per_head = pair_tasks + ((hd - rot) >> 2);
+  for (int task = threadIdx.x; task < n_heads * per_head; task += blockDim.x) {
+    const int head = task / per_head, k = task % per_head;
+    const float* src = src_row + (size_t)head * hd;
+    const bool is_v = head >= n_q_heads + n_kv_heads;
+    __nv_bfloat16* dst =
+        head < n_q_heads ? q_out + ((size_t)t * n_q_heads + head) * hd
+        : is_v ? cache + v_base + (size_t)(head - n_q_heads - n_kv_heads) * page_size * hd
+               : cache + k_base + (size_t)(head - n_q_heads) * page_size * hd;
+    if (k >= pair_tasks) {                           // beyond the rotated part: a copy
+      const int e = rot + 4 * (k - pair_tasks);
+      const float4 a = *reinterpret_cast<const float4*>(src + e);
+      store_bf16x4(dst + e, a.x, a.y, a.z, a.w);
+      continue;
+    }
+    const int e = 4 * k;
+    const float4 a = *reinterpret_cast<const float4*>(src + e);
+    const float4 b = *reinterpret_cast<const float4*>(src + e + half);
+    if (is_v) {
+      store_bf16x4(dst + e, a.x, a.y, a.z, a.w);
+      store_bf16x4(dst + e + half, b.x, b.y, b.z, b.w);
+    } else {
+      const float4 c = *reinterpret_cast<const float4*>(cs + e);
+      const float4 sn = *reinterpret_cast<const float4*>(cs + half + e);
+      store_bf16x4(dst + e, a.x * c.x - b.x * sn.x, a.y * c.y - b.y * sn.y, a.z * c.z - b.z * sn.z,
+                   a.w * c.w - b.w * sn.w);
+      store_bf16x4(dst + e + half, a.x * sn.x + b.x * c.x, a.y * sn.y + b.y * c.y,
+                   a.z * sn.z + b.z * c.z, a.w * sn.w + b.w * c.w);
+    }
+  }
+}
+
 extern "C" int sb_rope_store(const float* qkv, int n_rows, int n_q_heads, int n_kv_heads, int hd,
                              int rot, const float* inv_freq, const int32_t* row_seq,
                              const int32_t* row_pos, const int32_t* page_off,
@@ -320,6 +389,15 @@ extern "C" int sb_rope_store(const float* qkv, int n_rows, int n_q_heads, int n_
                   (TC*)cache, (TQ*)q_out, has_kv);
       });
     });
+    SB_CHECK_LAUNCH("sb_rope_store");
+    return SB_OK;
+  }
+  if (q_dtype == SB_BF16 && cache_dtype == SB_BF16 && (rot & 7) == 0 && ((hd - rot) & 3) == 0 &&
+      (((uintptr_t)qkv | (uintptr_t)inv_freq) & 15) == 0 &&
+      (((uintptr_t)q_out | (uintptr_t)cache) & 7) == 0) {
+    sb_launch(rope_store_vec_kernel, grid, dim3(threads), smem, stream, qkv, n_q_heads, n_kv_heads,
+              hd, rot, inv_freq, row_seq, row_pos, page_off, page_ids, page_size,
+              (__nv_bfloat16*)cache, (__nv_bfloat16*)q_out, has_kv);
     SB_CHECK_LAUNCH("sb_rope_store");
     return SB_OK;
   }
