@@ -50,7 +50,7 @@ def test_static_scratch_entry_point_matches_the_ordinary_one():
     for call, (lengths, seed) in enumerate([([700, 300, 1025, 64], 1), ([2000, 257], 2)]):
         cache, plan, storage, q = _setup(hq, hkv, hd, lengths, seed)
         want = torch.empty(len(lengths), hq * hd, dtype=torch.bfloat16, device=DEV)
-        ops.attention(q, want, plan, 0, storage, hq, hkv, hd, 0, hd ** -0.5)
+        ops.attention(q, want, plan, 0, storage, hq, hkv, hd, 0, hd ** -0.5, kernel="mma")   # the same kernel
         got = torch.full_like(want, float("nan"))
         g = plan.groups[0]
         rc = fn(ptr(q), ptr(got), len(lengths), plan.n_seqs, plan.max_new, ptr(plan.seq_row0),
