@@ -13,8 +13,8 @@ sys.path.insert(0, str(ROOT))
 sys.path.insert(0, str(Path(__file__).resolve().parent))
 
 # Three tiny configurations of the architecture that differ in every size and option:
-# layers, width, heads and groups (2:1, 6:1, 1:1), head size (16, 32, 48 with an explicit
-# head_dim that is not width/heads), intermediate size, vocabulary (none a power of two in B
+# layers, width, heads and groups (2:1, 6:1, 1:1), head size (16; 64 and 48 with an explicit
+# head_dim that is not width/heads; 64 runs the tensor-memory attention kernel), intermediate size, vocabulary (none a power of two in B
 # and C), rope base, norm eps, tied or separate head, and full or windowed attention.
 TINY = {
     "A": dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", hidden_size=64,
@@ -23,7 +23,7 @@ TINY = {
               tie_word_embeddings=True, use_sliding_window=False, max_position_embeddings=128,
               eos_token_id=7),
     "B": dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", hidden_size=192,
-              num_hidden_layers=3, num_attention_heads=6, num_key_value_heads=1,
+              num_hidden_layers=3, num_attention_heads=6, num_key_value_heads=1, head_dim=64,
               intermediate_size=512, vocab_size=1000, rope_theta=1000000.0, rms_norm_eps=1e-5,
               tie_word_embeddings=False, use_sliding_window=False, max_position_embeddings=256,
               eos_token_id=[998, 999]),
