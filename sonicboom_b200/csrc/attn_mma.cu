@@ -306,7 +306,6 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(const AttnP
   __shared__ int s_last;
   const uint32_t qs = (uint32_t)__cvta_generic_to_shared(smem);
   const uint32_t kv0 = qs + DEC_ROWS * LDS * 2;               // K0, V0, K1, V1
-  sb_pdl_launch();
   sb_pdl_wait();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
@@ -370,6 +369,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(const AttnP
     }
     cp_async_commit();
   }
+  sb_pdl_launch();                                    // the keys and values have been read
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
     l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
@@ -610,7 +610,7 @@ extern "C" int sb_attention(const void* q, void* out, int n_rows, int n_seqs, in
     if (need && (!counters || n_counters < n_seqs * n_kv_heads))
       SB_FAIL(SB_ERR_ARG, "sb_attention: %d zeroed counters needed, %d given", n_seqs * n_kv_heads,
               n_counters);
-    sb_launch(attn_decode_kernel, dim3(p.n_splits, n_kv_heads, n_seqs), dim3(DEC_WARPS * 32),
+    sb_launch<SB_K_ATTENTION>(attn_decode_kernel, dim3(p.n_splits, n_kv_heads, n_seqs), dim3(DEC_WARPS * 32),
               DECODE_SMEM, stream, p);
     SB_CHECK_LAUNCH("sb_attention (decode)");
     return SB_OK;
@@ -635,7 +635,7 @@ extern "C" int sb_attention(const void* q, void* out, int n_rows, int n_seqs, in
       SB_FAIL(SB_ERR_CUDA, "sb_attention: cuTensorMapEncodeTiled failed");
     const long tiles5 = ((long)max_new * G + T5_QT * T5_ROWS - 1) / (T5_QT * T5_ROWS);
     if (tiles5 > 2147483647L) SB_FAIL(SB_ERR_UNSUPPORTED, "sb_attention: too many rows");
-    sb_launch(attn_prefill_tc5_kernel, dim3((unsigned)tiles5, n_kv_heads, n_seqs),
+    sb_launch<SB_K_ATTENTION>(attn_prefill_tc5_kernel, dim3((unsigned)tiles5, n_kv_heads, n_seqs),
               dim3(T5_THREADS), T5_SMEM, stream, map_kv, p);
     SB_CHECK_LAUNCH("sb_attention (prefill, tcgen05)");
     if (tc5_checked) return SB_OK;
@@ -656,7 +656,7 @@ extern "C" int sb_attention(const void* q, void* out, int n_rows, int n_seqs, in
 #endif
   const long tiles = ((long)max_new * G + BM - 1) / BM;
   if (tiles > 2147483647L) SB_FAIL(SB_ERR_UNSUPPORTED, "sb_attention: too many rows");
-  sb_launch(attn_prefill_kernel, dim3((unsigned)tiles, n_kv_heads, n_seqs), dim3(PREFILL_THREADS), PREFILL_SMEM,
+  sb_launch<SB_K_ATTENTION>(attn_prefill_kernel, dim3((unsigned)tiles, n_kv_heads, n_seqs), dim3(PREFILL_THREADS), PREFILL_SMEM,
             stream, p);
   SB_CHECK_LAUNCH("sb_attention (prefill)");
   return SB_OK;
@@ -749,7 +749,7 @@ extern "C" int sb_attention_decode_static(const void* q, void* out, int n_rows, 
   p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads; p.window = window; p.n_splits = n_splits;
   p.n_seqs = n_seqs;
   p.scale_log2 = scale * LOG2E;
-  sb_launch(attn_decode_kernel, dim3(n_splits, n_kv_heads, n_seqs), dim3(DEC_WARPS * 32), DECODE_SMEM,
+  sb_launch<SB_K_ATTENTION>(attn_decode_kernel, dim3(n_splits, n_kv_heads, n_seqs), dim3(DEC_WARPS * 32), DECODE_SMEM,
             stream, p);
   SB_CHECK_LAUNCH("sb_attention_decode_static (decode)");
   return SB_OK;

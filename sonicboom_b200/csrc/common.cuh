@@ -66,23 +66,31 @@ __device__ __forceinline__ float sb_warp_max(float v) {
   return v;
 }
 
-// Programmatic dependent launch (optional, see sb_pdl_enabled): every kernel of a step can be
-// launched so that it may start while its predecessor in the stream is still running.  A kernel calls sb_pdl_launch() early
-// (its successor may then be scheduled as soon as resources free up) and sb_pdl_wait() before
-// it first touches anything a predecessor wrote; what it does before the wait (barrier set-up,
-// prefetching weights) overlaps the predecessor's tail.  Without the launch attribute both are
-// no-ops.
+// Programmatic dependent launch (optional, see sb_pdl_enabled): a kernel launched this way may
+// start while its predecessor in the stream is still running.  A kernel calls sb_pdl_wait()
+// before it first touches anything a predecessor wrote; what it does before the wait (barrier
+// set-up, requesting weights) overlaps the predecessor's tail.  It calls sb_pdl_launch() where
+// its successor may be scheduled: small kernels at their start, the products and the attention
+// once their own operands have been requested, so that a successor does not take resources the
+// kernel still wants.  Without the launch attribute both are no-ops.
 __device__ __forceinline__ void sb_pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 __device__ __forceinline__ void sb_pdl_launch() {
   asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
 }
 
-extern "C" int sb_pdl_enabled();      // per library: 0 off, 1 every kernel, 2 only kernels that
-                                      // prefetch weights before their wait; set with sb_set_pdl
+// Kernel classes, as bits of the mask that says which kernels get the launch attribute.
+enum SbKernelClass {
+  SB_K_TC5 = 1,          // tcgen05 products
+  SB_K_SKINNY = 2,       // weight-streaming and tiled mma.sync products
+  SB_K_ATTENTION = 4,
+  SB_K_ELEMENTWISE = 8,  // embedding, norms, rotation, casts, small adds
+  SB_K_REDUCE = 16,      // the split-K reduce of the tcgen05 product
+  SB_K_OTHER = 32        // sampler, plain kernels
+};
 
-// `prefetches`: the kernel requests weights before its dependency wait (it gains from an early
-// start even when its neighbours do not).
-template <bool prefetches = false, typename... Exp, typename... Act>
+extern "C" int sb_pdl_enabled();      // per library: the mask of kernel classes; set with sb_set_pdl
+
+template <int CLS = SB_K_OTHER, typename... Exp, typename... Act>
 inline cudaError_t sb_launch(void (*kernel)(Exp...), dim3 grid, dim3 block, size_t smem,
                              cudaStream_t stream, Act&&... args) {
   cudaLaunchConfig_t cfg = {};
@@ -94,8 +102,7 @@ inline cudaError_t sb_launch(void (*kernel)(Exp...), dim3 grid, dim3 block, size
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  const int level = sb_pdl_enabled();
-  cfg.numAttrs = (level == 1 || (level == 2 && prefetches)) ? 1 : 0;
+  cfg.numAttrs = (sb_pdl_enabled() & CLS) ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<Exp>(args)...);
 }
 

@@ -26,7 +26,7 @@ extern "C" int sb_embed(const int32_t* tokens, int n_rows, const void* table, in
   if (n_rows <= 0 || width <= 0) SB_FAIL(SB_ERR_ARG, "sb_embed: n_rows=%d width=%d", n_rows, width);
   if (!sb_valid_dtype(table_dtype)) SB_FAIL(SB_ERR_ARG, "sb_embed: table dtype %d", table_dtype);
   SB_DISPATCH_DTYPE(table_dtype, TW, {
-    sb_launch(embed_kernel<TW>, dim3(n_rows), dim3(256), 0, stream, tokens, (const TW*)table, width, out);
+    sb_launch<SB_K_ELEMENTWISE>(embed_kernel<TW>, dim3(n_rows), dim3(256), 0, stream, tokens, (const TW*)table, width, out);
   });
   SB_CHECK_LAUNCH("sb_embed");
   return SB_OK;
@@ -161,10 +161,10 @@ extern "C" int sb_rmsnorm(const float* x, const int32_t* rows, int n_rows, int w
   SB_DISPATCH_DTYPE(weight_dtype, TW, {
     SB_DISPATCH_DTYPE(out_dtype, TO, {
       if (vec)
-        sb_launch(rmsnorm_vec_kernel<TW, TO>, dim3(n_rows), dim3(NORM_THREADS), 0, stream, x, rows,
+        sb_launch<SB_K_ELEMENTWISE>(rmsnorm_vec_kernel<TW, TO>, dim3(n_rows), dim3(NORM_THREADS), 0, stream, x, rows,
                   (const TW*)weight, width, eps, (TO*)out);
       else
-        sb_launch(rmsnorm_kernel<TW, TO>, dim3(n_rows), dim3(threads), 0, stream, x, rows,
+        sb_launch<SB_K_ELEMENTWISE>(rmsnorm_kernel<TW, TO>, dim3(n_rows), dim3(threads), 0, stream, x, rows,
                   (const TW*)weight, width, eps, (TO*)out);
     });
   });
@@ -190,7 +190,7 @@ extern "C" int sb_cast(const void* in, int in_dtype, void* out, int out_dtype, s
   const int blocks = (int)((n + 255) / 256 < 4096 ? (n + 255) / 256 : 4096);
   SB_DISPATCH_DTYPE(in_dtype, TI, {
     SB_DISPATCH_DTYPE(out_dtype, TO, {
-      sb_launch(cast_kernel<TI, TO>, dim3(blocks), dim3(256), 0, stream, (const TI*)in, (TO*)out, n);
+      sb_launch<SB_K_ELEMENTWISE>(cast_kernel<TI, TO>, dim3(blocks), dim3(256), 0, stream, (const TI*)in, (TO*)out, n);
     });
   });
   SB_CHECK_LAUNCH("sb_cast");
@@ -384,7 +384,7 @@ extern "C" int sb_rope_store(const float* qkv, int n_rows, int n_q_heads, int n_
     const int hthreads = hd >= 128 ? 128 : (hd >= 64 ? 64 : 32);
     SB_DISPATCH_DTYPE(q_dtype, TQ, {
       SB_DISPATCH_DTYPE(cache_dtype, TC, {
-        sb_launch(rope_store_head_kernel<TQ, TC>, hgrid, dim3(hthreads), 0, stream, qkv, n_q_heads,
+        sb_launch<SB_K_ELEMENTWISE>(rope_store_head_kernel<TQ, TC>, hgrid, dim3(hthreads), 0, stream, qkv, n_q_heads,
                   n_kv_heads, hd, rot, inv_freq, row_seq, row_pos, page_off, page_ids, page_size,
                   (TC*)cache, (TQ*)q_out, has_kv);
       });
@@ -395,7 +395,7 @@ extern "C" int sb_rope_store(const float* qkv, int n_rows, int n_q_heads, int n_
   if (q_dtype == SB_BF16 && cache_dtype == SB_BF16 && (rot & 7) == 0 && ((hd - rot) & 3) == 0 &&
       (((uintptr_t)qkv | (uintptr_t)inv_freq) & 15) == 0 &&
       (((uintptr_t)q_out | (uintptr_t)cache) & 7) == 0) {
-    sb_launch(rope_store_vec_kernel, grid, dim3(threads), smem, stream, qkv, n_q_heads, n_kv_heads,
+    sb_launch<SB_K_ELEMENTWISE>(rope_store_vec_kernel, grid, dim3(threads), smem, stream, qkv, n_q_heads, n_kv_heads,
               hd, rot, inv_freq, row_seq, row_pos, page_off, page_ids, page_size,
               (__nv_bfloat16*)cache, (__nv_bfloat16*)q_out, has_kv);
     SB_CHECK_LAUNCH("sb_rope_store");
@@ -403,7 +403,7 @@ extern "C" int sb_rope_store(const float* qkv, int n_rows, int n_q_heads, int n_
   }
   SB_DISPATCH_DTYPE(q_dtype, TQ, {
     SB_DISPATCH_DTYPE(cache_dtype, TC, {
-      sb_launch(rope_store_kernel<TQ, TC>, grid, dim3(threads), smem, stream,
+      sb_launch<SB_K_ELEMENTWISE>(rope_store_kernel<TQ, TC>, grid, dim3(threads), smem, stream,
           qkv, n_q_heads, n_kv_heads, hd, rot, inv_freq, row_seq, row_pos, page_off, page_ids,
           page_size, (TC*)cache, (TQ*)q_out, has_kv);
     });

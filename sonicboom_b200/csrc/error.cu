@@ -17,19 +17,19 @@ void sb_set_error(const char* fmt, ...) {
 }
 
 
-// Whether kernels are launched with programmatic dependent launch: SB_PDL=0 never, 1 every
-// kernel, 2 only the tcgen05 products (which request weights before their wait).  Off by default: on
-// B200 the decode step of the 7B-sized model measured slower with it (the many small blocks of
-// the weight-streaming product gain nothing from starting early and delay their neighbours),
-// while the tcgen05 products alone gain a few percent.
+// Which kernels are launched with programmatic dependent launch: a mask of SbKernelClass bits
+// (SB_PDL=<number> in the environment, sb_set_pdl at run time; 0 = none, 63 = all).  The
+// default is every class but the weight-streaming products: on B200 the decode step of the
+// 7B-sized model gains 4-5 % that way at batch 1 and 8 (1 % at batch 64 and in prefill), and
+// loses about 10 % when the weight-streaming products are launched this way as well.
 static int g_pdl = -1;
 
 extern "C" int sb_pdl_enabled() {
   if (g_pdl < 0) {
     const char* e = getenv("SB_PDL");
-    g_pdl = (e && e[0] >= '0' && e[0] <= '2') ? e[0] - '0' : 0;
+    g_pdl = e ? atoi(e) & 63 : (63 & ~SB_K_SKINNY);
   }
   return g_pdl;
 }
 
-extern "C" void sb_set_pdl(int level) { g_pdl = level < 0 ? 0 : (level > 2 ? 2 : level); }
+extern "C" void sb_set_pdl(int mask) { g_pdl = mask & 63; }

@@ -65,7 +65,6 @@ gemm_skinny_kernel(const bf16* X, const bf16* __restrict__ W, int M, int N, int 
                    int epilogue, const void* __restrict__ bias, int bias_dtype,
                    const float* residual, TO* out) {
   __shared__ float partial[SK_WARPS][NT][32][4];
-  sb_pdl_launch();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int m0 = blockIdx.x * 16;
   const uint4* w0 = (const uint4*)(W + (size_t)min(m0 + g, N - 1) * K) + t;
@@ -110,6 +109,7 @@ gemm_skinny_kernel(const bf16* X, const bf16* __restrict__ W, int M, int N, int 
     }
   }
   if (warp >= n_blocks) sb_pdl_wait();          // a warp without K blocks never waited above
+  sb_pdl_launch();                              // the weights have been read
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
@@ -149,7 +149,7 @@ int launch_skinny(const bf16* X, const bf16* W, int M, int N, int K, int epilogu
                   int out_dtype, cudaStream_t stream) {
   const int blocks = (N + 15) / 16;
   SB_DISPATCH_DTYPE(out_dtype, TO, {
-    sb_launch(gemm_skinny_kernel<NT, TO>, dim3(blocks), dim3(SK_WARPS * 32), 0, stream,
+    sb_launch<SB_K_SKINNY>(gemm_skinny_kernel<NT, TO>, dim3(blocks), dim3(SK_WARPS * 32), 0, stream,
         X, W, M, N, K, epilogue, bias, bias_dtype, residual, (TO*)out);
   });
   SB_CHECK_LAUNCH("sb_gemm_skinny");
@@ -350,7 +350,7 @@ extern "C" int sb_gemm_tiled(const void* A, int a_dtype, const void* W, int w_dt
         SB_FAIL(SB_ERR_CUDA, "sb_gemm_tiled: shared memory opt-in failed: %s", cudaGetErrorString(e));
       configured[out_dtype] = true;
     }
-    sb_launch(gemm_tiled_kernel<TO>, grid, dim3(TILED_THREADS), TILED_SMEM, stream,
+    sb_launch<SB_K_SKINNY>(gemm_tiled_kernel<TO>, grid, dim3(TILED_THREADS), TILED_SMEM, stream,
         (const bf16*)A, (const bf16*)W, M, N, K, epilogue, bias, bias_dtype, residual, (TO*)out);
   });
   SB_CHECK_LAUNCH("sb_gemm_tiled");

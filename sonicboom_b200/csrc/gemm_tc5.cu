@@ -125,7 +125,6 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   volatile uint32_t* tmem_slot_ptr =
       (volatile uint32_t*)(smem_raw + (tmem_slot - raw));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  sb_pdl_launch();
   // consecutive blocks walk the A tiles of one B tile (or K splits first, in the swapped form),
   // so that a wave of blocks shares its operand tiles through L2
   int tile_a, tile_b, split = 0;
@@ -188,6 +187,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       tma_load_2d(b_dst, &map_b, (k_begin + i) * BK, tile_b * BN, full0 + 8 * s);
       issued = i + 1;
     }
+    sb_pdl_launch();                        // every load of this block is on its way
     if (!ok) {
       // let copies that are still in flight land before the block's memory goes away
       for (int i = max(0, issued - STAGES); i < issued; ++i)
@@ -472,7 +472,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const Tc5Params& p, int
       SB_FAIL(SB_ERR_CUDA, "sb_gemm_tc5: shared memory opt-in failed: %s", cudaGetErrorString(e));
     configured = true;
   }
-  sb_launch<true>(gemm_tc5_kernel<BN, STAGES, SWAPPED, TO>, dim3(blocks), dim3(THREADS), smem, stream,
+  sb_launch<SB_K_TC5>(gemm_tc5_kernel<BN, STAGES, SWAPPED, TO>, dim3(blocks), dim3(THREADS), smem, stream,
                   ma, mb, p);
   SB_CHECK_LAUNCH("sb_gemm_tc5");
   return SB_OK;
@@ -490,7 +490,7 @@ int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, const Tc5Par
       SB_FAIL(SB_ERR_CUDA, "sb_gemm_tc5: shared memory opt-in failed: %s", cudaGetErrorString(e));
     configured = true;
   }
-  sb_launch(gemm_tc5_persistent_kernel<BN, STAGES, TO>, dim3(blocks), dim3(THREADS), smem, stream, ma,
+  sb_launch<SB_K_TC5>(gemm_tc5_persistent_kernel<BN, STAGES, TO>, dim3(blocks), dim3(THREADS), smem, stream, ma,
             mb, p);
   SB_CHECK_LAUNCH("sb_gemm_tc5 (persistent)");
   return SB_OK;
@@ -622,8 +622,8 @@ extern "C" int sb_gemm_tc5(const void* A, int a_dtype, const void* W, int w_dtyp
   const int n_out = epilogue == SB_EPI_SWIGLU ? N / 2 : N;
   const long work = (long)((n_out + 3) / 4) * M;
   const dim3 rgrid((unsigned)((work + 255) / 256));
-  if (out_dtype == SB_F32) sb_launch(tc5_reduce_kernel<float>, rgrid, dim3(256), 0, stream, p, bn);
-  else sb_launch(tc5_reduce_kernel<bf16>, rgrid, dim3(256), 0, stream, p, bn);
+  if (out_dtype == SB_F32) sb_launch<SB_K_REDUCE>(tc5_reduce_kernel<float>, rgrid, dim3(256), 0, stream, p, bn);
+  else sb_launch<SB_K_REDUCE>(tc5_reduce_kernel<bf16>, rgrid, dim3(256), 0, stream, p, bn);
   SB_CHECK_LAUNCH("sb_gemm_tc5 (reduce)");
   return SB_OK;
 }

@@ -201,9 +201,13 @@ def _tc5_workspace(M: int, N: int, K: int, device):
     return bufs[-1]
 
 
+PDL_TC5, PDL_SKINNY, PDL_ATTENTION, PDL_ELEMENTWISE, PDL_REDUCE, PDL_OTHER, PDL_ALL = 1, 2, 4, 8, 16, 32, 63
+
+
 def set_pdl(level) -> None:
-    """Programmatic dependent launch of the kernels: 0 (or False) off, 1 (or True) every
-    kernel, 2 only the tcgen05 products.  The environment variable SB_PDL sets it at start."""
+    """Which kernels are launched with programmatic dependent launch: a mask of the PDL_* bits
+    (0 none, PDL_ALL every kernel; the default is every class but PDL_SKINNY).  The
+    environment variable SB_PDL sets it at start."""
     level = int(level)
     lib().sb_set_pdl(level)
     for l in _attn_libs.values():
