@@ -32,15 +32,9 @@
 
 namespace {
 
-#ifndef SB_T5_STAGES
-#define SB_T5_STAGES 3
-#endif
-#ifndef SB_T5_QT
-#define SB_T5_QT 2
-#endif
 constexpr int T5_ROWS = 128;                                // rows of a query tile = UMMA M
-constexpr int T5_QT = SB_T5_QT;                             // query tiles per block
-constexpr int T5_ST = SB_T5_STAGES;                         // depth of the K ring and of the V ring
+constexpr int T5_QT = 2;                                    // query tiles per block
+constexpr int T5_ST = 3;                                    // depth of the K ring and of the V ring
 constexpr int T5_THREADS = 64 + 128 * T5_QT + 32 * (T5_QT - 1);   // + the other tiles' MMA warps
 constexpr int T5_SUB = HD / 64 > 0 ? HD / 64 : 1;            // 64-wide pieces of a head
 constexpr uint32_t T5_Q_BYTES = T5_SUB * T5_ROWS * 128;     // one query tile
@@ -50,10 +44,7 @@ constexpr uint32_t T5_SMEM =
     T5_QT * T5_Q_BYTES + 2 * T5_ST * T5_KV_BYTES + 2 * T5_QT * T5_P_BYTES + 512;
 constexpr uint32_t T5_TILE_COLS = 2 * KT + HD;              // tensor memory of a query tile: S0 S1 O
 constexpr uint32_t T5_TMEM_COLS = T5_QT * T5_TILE_COLS <= 256 ? 256 : 512;
-#ifndef SB_T5_LAZY
-#define SB_T5_LAZY 8.0f
-#endif
-constexpr float T5_LAZY = SB_T5_LAZY;                             // log2 of how far a maximum may run ahead
+constexpr float T5_LAZY = 8.0f;                             // log2 of how far a maximum may run ahead
 static_assert(T5_QT * T5_TILE_COLS <= 512, "tensor memory has 512 columns");
 
 // barriers: the rings first (a stage is free when every query tile's product that read it has

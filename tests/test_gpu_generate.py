@@ -70,6 +70,27 @@ def test_greedy_generation_of_a_batch(model_dirs, oracles, name, dtype):
         assert alone == outs and small == outs
 
 
+def test_dependent_launch_changes_no_token(model_dirs):
+    """The kernels of a step may overlap through programmatic dependent launch; with it off,
+    on for the default kernel classes, and on for every kernel the same tokens come out
+    bit for bit (each kernel waits before it touches what a predecessor wrote), and no bounded
+    wait of the tensor-memory kernels gives up."""
+    from sonicboom_b200 import ops
+    model = llm.model_load(model_dirs["B"], dtype="bfloat16")
+    prompts = prompts_for("B", [3, 40, 90, 129], seed=9)
+    default = ops.lib().sb_pdl_enabled()
+    outs = {}
+    try:
+        for mask in (0, default, ops.PDL_ALL):
+            ops.set_pdl(mask)
+            outs[mask] = llm.generate_batch(model, prompts, max_tokens=24, ignore_eos=True)
+    finally:
+        ops.set_pdl(default)
+    assert outs[0] == outs[default] == outs[ops.PDL_ALL]
+    assert default == ops.PDL_ALL & ~ops.PDL_SKINNY
+    assert ops.tc5_status() == 0 and ops.attention_status(TINY["B"]["head_dim"]) == 0
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_stop_tokens_and_eos(model_dirs, oracles, dtype):
     model = llm.model_load(model_dirs["A"], dtype=dtype)
