@@ -306,10 +306,13 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(const AttnP
   __shared__ int s_last;
   const uint32_t qs = (uint32_t)__cvta_generic_to_shared(smem);
   const uint32_t kv0 = qs + DEC_ROWS * LDS * 2;               // K0, V0, K1, V1
-  sb_pdl_wait();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int G = p.n_q_heads / p.n_kv_heads;
+  // The step's plan (rows, positions, pages) was written before the step's first kernel, and
+  // cache pages that lie wholly before the new positions in earlier steps: none of that
+  // needs the wait for the kernel before this one, which wrote the query rows and the new
+  // positions' keys and values.
   const int row0 = p.seq_row0[b], n_new = p.seq_row0[b + 1] - row0, pos0 = p.seq_pos0[b];
   const int R = n_new * G;
   const int p_hi = pos0 + n_new - 1;
@@ -319,7 +322,18 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(const AttnP
   const int32_t* pages = p.page_ids + p.page_off[b];
   const int tile_lo = max(split * SPLIT_PAGES, key_lo / KT);
   const int tile_hi = min(split * SPLIT_PAGES + SPLIT_PAGES - 1, p_hi / KT);
-
+  // the split's page ids are read together
+  int page_of[SPLIT_PAGES];
+#pragma unroll
+  for (int i = 0; i < SPLIT_PAGES; ++i)
+    page_of[i] = tile_lo + i <= tile_hi ? pages[tile_lo + i] : 0;
+  const bool first_is_old = (tile_lo + 1) * KT <= pos0;
+  if (first_is_old)
+    load_kv_tile(kv0, kv0 + KT * LDS * 2, p.cache, page_of[0], p.n_kv_heads, kvh, tid, DEC_WARPS * 32);
+  sb_pdl_wait();
+  if (!first_is_old)
+    load_kv_tile(kv0, kv0 + KT * LDS * 2, p.cache, page_of[0], p.n_kv_heads, kvh, tid, DEC_WARPS * 32);
+  cp_async_commit();                                  // group: the first tile
   for (int idx = tid; idx < DEC_ROWS * (HD / 8); idx += DEC_WARPS * 32) {
     const int row = idx / (HD / 8), ch = idx % (HD / 8);
     const bool valid = row < R;
@@ -327,17 +341,11 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(const AttnP
     cp_async16(qs + (uint32_t)(row * LDS + ch * 8) * 2,
                p.q + ((size_t)(row0 + t) * p.n_q_heads + kvh * G + g) * HD + ch * 8, valid);
   }
-  // the split's page ids are read together, and its first two tiles are requested at once
-  int page_of[SPLIT_PAGES];
-#pragma unroll
-  for (int i = 0; i < SPLIT_PAGES; ++i)
-    page_of[i] = tile_lo + i <= tile_hi ? pages[tile_lo + i] : 0;
-  load_kv_tile(kv0, kv0 + KT * LDS * 2, p.cache, page_of[0], p.n_kv_heads, kvh, tid, DEC_WARPS * 32);
-  cp_async_commit();
+  cp_async_commit();                                  // group: the query rows
   if (tile_lo < tile_hi)
     load_kv_tile(kv0 + 2 * KT * LDS * 2, kv0 + 3 * KT * LDS * 2, p.cache, page_of[1], p.n_kv_heads, kvh,
                  tid, DEC_WARPS * 32);
-  cp_async_commit();
+  cp_async_commit();                                  // group: the second tile
 
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
   float o[HD / 8][4];
