@@ -109,9 +109,9 @@ rmsnorm_vec_kernel(const float* x, const int32_t* rows, const TW* __restrict__ w
   __shared__ float warp_sums[NORM_THREADS / 32];
   __shared__ float inv_shared;
   sb_pdl_launch();
-  sb_pdl_wait();
   const int r = blockIdx.x;
-  const float* xr = x + (size_t)(rows ? rows[r] : r) * width;
+  const float* xr = x + (size_t)(rows ? rows[r] : r) * width;     // `rows` is part of the step's plan
+  sb_pdl_wait();
   float v[NORM_VEC][4];
   float s = 0.0f;
 #pragma unroll
@@ -216,30 +216,46 @@ __global__ void rope_store_head_kernel(const float* qkv, int n_q_heads, int n_kv
                                        const int32_t* page_off, const int32_t* page_ids,
                                        int page_size, TC* cache, TQ* q_out, int has_kv) {
   sb_pdl_launch();
-  sb_pdl_wait();
   const int t = blockIdx.x;
   const int head = blockIdx.y;                       // q heads, then k heads, then v heads
   const int width_in = (n_q_heads + (has_kv ? 2 * n_kv_heads : 0)) * hd;
   const float* src = qkv + (size_t)t * width_in + (size_t)head * hd;
-  const int pos = row_pos[t];
   const int half = rot >> 1;
   const bool is_v = head >= n_q_heads + n_kv_heads;
+  // The position, the page and the angles come from the step's plan, which was complete
+  // before the step's first kernel: they are worked out before the wait for the kernel that
+  // writes q|k|v.
+  const int pos = row_pos[t];
+  size_t dst_row = 0;
+  if (head >= n_q_heads) {
+    const int page = page_ids[page_off[row_seq[t]] + pos / page_size];
+    const int kvh = is_v ? head - n_q_heads - n_kv_heads : head - n_q_heads;
+    dst_row = (((size_t)page * 2 + (is_v ? 1 : 0)) * n_kv_heads + kvh) * page_size + pos % page_size;
+  }
+  float c0 = 1.0f, sn0 = 0.0f;                       // of this thread's first element
+  if (!is_v && (int)threadIdx.x < rot) {
+    const int i = (int)threadIdx.x < half ? threadIdx.x : threadIdx.x - half;
+    const float theta = (float)pos * inv_freq[i];
+    c0 = cosf(theta);
+    sn0 = sinf(theta);
+  }
+  sb_pdl_wait();
   for (int e = threadIdx.x; e < hd; e += blockDim.x) {
     float v = src[e];
     if (!is_v && e < rot) {
-      const int i = e < half ? e : e - half;
-      const float theta = (float)pos * inv_freq[i];
-      const float c = cosf(theta), sn = sinf(theta);
+      float c = c0, sn = sn0;
+      if (e != (int)threadIdx.x) {
+        const int i = e < half ? e : e - half;
+        const float theta = (float)pos * inv_freq[i];
+        c = cosf(theta);
+        sn = sinf(theta);
+      }
       v = e < half ? src[e] * c - src[e + half] * sn : src[e - half] * sn + src[e] * c;
     }
-    if (head < n_q_heads) {
+    if (head < n_q_heads)
       q_out[((size_t)t * n_q_heads + head) * hd + e] = sb_from_f32<TQ>(v);
-    } else {
-      const int page = page_ids[page_off[row_seq[t]] + pos / page_size];
-      const int kvh = is_v ? head - n_q_heads - n_kv_heads : head - n_q_heads;
-      cache[((((size_t)page * 2 + (is_v ? 1 : 0)) * n_kv_heads + kvh) * page_size + pos % page_size) *
-                hd + e] = sb_from_f32<TC>(v);
-    }
+    else
+      cache[dst_row * hd + e] = sb_from_f32<TC>(v);
   }
 }
 
