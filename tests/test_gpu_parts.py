@@ -1,6 +1,7 @@
 """Each part alone against the plain implementation, the run order as data (a layer twice, a
 layer reading another's cache), and a toy mixer with state of its own that is registered,
-built and stepped without a change to the package."""
+built and stepped without a change to the package; likewise a toy feed-forward that routes
+rows to experts and a toy position encoding."""
 import dataclasses
 
 import pytest
@@ -220,6 +221,153 @@ def test_a_toy_mixer_with_state_registers_builds_and_steps(dtype):
                 eng.close(s)
     finally:
         parts.MIXERS.pop("running_mean")
+
+
+# --------------------------- a toy feed-forward with routing and a toy position encoding
+
+class Top1Experts(parts.FeedForward):
+    """Every row goes to the one expert its router score is highest for (float32 scores, the
+    lowest index on a tie); an expert is a gated feed-forward of its own.  Experts run on the
+    rows routed to them, gathered, through the package's product kernels."""
+
+    def __init__(self, spec, dtype, device):
+        self.spec, self.dtype = spec, dtype
+        self.n_experts = dict(spec.params)["experts"]
+        self.router = self.w_gate_up = self.w_down = None
+
+    def tensor_requests(self):
+        p, d, ff = self.spec.prefix, self.spec.width, self.spec.intermediate
+        reqs = [TensorRequest(p + "router.weight", (self.n_experts, d))]
+        for e in range(self.n_experts):
+            reqs += [TensorRequest(f"{p}experts.{e}.gate.weight", (ff, d)),
+                     TensorRequest(f"{p}experts.{e}.up.weight", (ff, d)),
+                     TensorRequest(f"{p}experts.{e}.down.weight", (d, ff))]
+        return reqs
+
+    def bind(self, get):
+        from sonicboom_b200.parts.feedforward import interleave_gate_up
+        p = self.spec.prefix
+        self.router = get(p + "router.weight").float()
+        self.w_gate_up = [interleave_gate_up(get(f"{p}experts.{e}.gate.weight"), get(f"{p}experts.{e}.up.weight"))
+                          for e in range(self.n_experts)]
+        self.w_down = [get(f"{p}experts.{e}.down.weight") for e in range(self.n_experts)]
+
+    def forward(self, h, ctx, residual=None):
+        from sonicboom_b200 import ops
+        choice = (h.float() @ self.router.t()).argmax(dim=1)
+        out = residual if residual is not None else torch.zeros(h.shape[0], self.spec.width, device=h.device)
+        for e in range(self.n_experts):
+            rows = (choice == e).nonzero().flatten()
+            if rows.numel() == 0:
+                continue
+            x = h[rows].contiguous()
+            t = torch.empty(x.shape[0], self.spec.intermediate, dtype=self.dtype, device=h.device)
+            ops.linear(x, self.w_gate_up[e], t, ops.EPI_SWIGLU)
+            y = torch.zeros(x.shape[0], self.spec.width, device=h.device)
+            ops.linear(t, self.w_down[e], y)
+            out[rows] += y
+        return out
+
+
+class HalfSpeedRotary(parts.PositionEncoding):
+    """Rotates the first half of a head with positions counted at half speed: another table for
+    the same rotation kernel."""
+
+    def __init__(self, spec, dtype, device):
+        self.head_dim, self.rotary_dim = spec.head_dim, spec.head_dim // 2
+        i = torch.arange(self.rotary_dim // 2, dtype=torch.float32)
+        self.inv_freq = (0.5 * torch.exp(-2.0 * i / self.rotary_dim * torch.log(torch.tensor(spec.theta)))).to(device)
+
+
+def half_speed_rope(x, positions, theta):
+    """Plain counterpart of HalfSpeedRotary on [n, heads, hd]."""
+    hd = x.shape[-1]
+    rot = pm.rope_neox(x[..., :hd // 2], positions.float() * 0.5, theta)
+    return torch.cat([rot, x[..., hd // 2:]], dim=-1)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_toy_routed_feed_forward_and_position_encoding(dtype):
+    """A feed-forward that routes rows to experts and a position encoding with its own table,
+    both defined here, are registered, built from a spec, given random weights and stepped
+    (prompt in two cuts, then single tokens) without a change to the package."""
+    parts.register_feed_forward("top1_experts", Top1Experts)
+    parts.register_position_encoding("half_speed", HalfSpeedRotary)
+    try:
+        width, vocab, hd = 64, 101, 32
+        layers = []
+        for i in range(2):
+            p = f"toy.layers.{i}."
+            mixer = MixerSpec(kind="attention", width=width, n_heads=2, n_kv_heads=1, head_dim=hd,
+                              scale=hd ** -0.5, qkv_bias=False, prefix=p + "self_attn.",
+                              position=PositionSpec("half_speed" if i == 0 else "rope_neox", hd, 3000.0))
+            ff = (FeedForwardSpec("top1_experts", width, 48, prefix=p + "moe.", params=(("experts", 3),))
+                  if i == 0 else FeedForwardSpec("swiglu", width, 80, prefix=p + "mlp."))
+            layers.append(LayerSpec("pre_norm", mixer, NormSpec("rmsnorm", width, 1e-6, p + "n1.weight"), ff,
+                                    NormSpec("rmsnorm", width, 1e-6, p + "n2.weight")))
+        spec = ModelSpec("Toy2", width, vocab, 256, "toy.embed.weight", tuple(layers),
+                         (ScheduleEntry(0), ScheduleEntry(1)),
+                         NormSpec("rmsnorm", width, 1e-6, "toy.norm.weight"), None)
+        model = DecoderModel(spec, DT[dtype], DEV)
+        src = RandomSource(model.tensor_requests(), seed=8, std=0.1, norm_std=0.1)
+        check(src, model.tensor_requests())
+        t = {n: src.tensor(n).float().cpu() for n in src.names()}
+        model.bind(lambda n: fetch(src, n, model.dtype, model.device))
+
+        def reference(tokens):
+            n = len(tokens)
+            pos = torch.arange(n)
+            x = pm.embedding(t["toy.embed.weight"], tokens)
+            for i in range(2):
+                p = f"toy.layers.{i}."
+                h = pm.rms_norm(x, t[p + "n1.weight"], 1e-6)
+                a = p + "self_attn."
+                q = pm.linear(h, t[a + "q_proj.weight"]).view(n, 2, hd)
+                k = pm.linear(h, t[a + "k_proj.weight"]).view(n, 1, hd)
+                v = pm.linear(h, t[a + "v_proj.weight"]).view(n, 1, hd)
+                if i == 0:
+                    q, k = half_speed_rope(q, pos, 3000.0), half_speed_rope(k, pos, 3000.0)
+                else:
+                    q, k = pm.rope_neox(q, pos, 3000.0), pm.rope_neox(k, pos, 3000.0)
+                x = x + pm.linear(pm.attention(q, k, v, pos, pos, hd ** -0.5).reshape(n, 2 * hd), t[a + "o_proj.weight"])
+                f = pm.rms_norm(x, t[p + "n2.weight"], 1e-6)
+                if i == 0:
+                    m = p + "moe."
+                    choice = (f @ t[m + "router.weight"].t()).argmax(dim=1)
+                    y = torch.zeros_like(x)
+                    for e in range(3):
+                        rows = choice == e
+                        y[rows] = pm.swiglu_mlp(f[rows], t[f"{m}experts.{e}.gate.weight"],
+                                                t[f"{m}experts.{e}.up.weight"], t[f"{m}experts.{e}.down.weight"])
+                    x = x + y
+                else:
+                    x = x + pm.swiglu_mlp(f, t[p + "mlp.gate_proj.weight"], t[p + "mlp.up_proj.weight"],
+                                          t[p + "mlp.down_proj.weight"])
+            return pm.linear(pm.rms_norm(x, t["toy.norm.weight"], 1e-6), t["toy.embed.weight"]), None
+
+        eng = sb.Engine(model, max_tokens=512)
+        g = torch.Generator().manual_seed(3)
+        reqs = [torch.randint(0, vocab, (n,), generator=g).tolist() for n in (70, 9)]
+        slots = [eng.open() for _ in reqs]
+        cuts = [40, 5]
+        got = [[], []]
+        out = eng.step([(s, r[:c], list(range(c))) for s, r, c in zip(slots, reqs, cuts)]).cpu()
+        got[0].append(out[:cuts[0]]); got[1].append(out[cuts[0]:])
+        out = eng.step([(s, r[c:c + 2], [0, 1]) for s, r, c in zip(slots, reqs, cuts)]).cpu()
+        got[0].append(out[:2]); got[1].append(out[2:])
+        for step in range(2, 4):                    # then a token each
+            out = eng.step([(s, [r[c + step]], [0]) for s, r, c in zip(slots, reqs, cuts)]).cpu()
+            got[0].append(out[:1]); got[1].append(out[1:])
+        for r, c, pieces in zip(reqs, cuts, got):
+            ref, _ = reference(r[:c + 4])
+            # a row whose two best router scores nearly tie may go to the other expert in bfloat16
+            err = (torch.cat(pieces) - ref).abs().amax(dim=1) / ref.abs().max()
+            assert float(err.median()) < TOL[dtype] and float((err < TOL[dtype]).float().mean()) > 0.9, err
+            if dtype == "float32":
+                assert float(err.max()) < TOL[dtype]
+    finally:
+        parts.FEED_FORWARDS.pop("top1_experts")
+        parts.POSITION_ENCODINGS.pop("half_speed")
 
 
 def test_unknown_kinds_are_refused():
