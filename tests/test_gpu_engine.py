@@ -69,6 +69,28 @@ def test_long_decoding(model_dirs, oracles, name, dtype):
     assert float(per_pos.max()) < TOL[dtype], f"worst position {int(per_pos.argmax())}"
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_long_context(tmp_path, dtype):
+    """Two requests of 1,800 and 700 tokens (29 and 11 cache pages) on configuration B with
+    room for 2,048 positions: the prompts in one step, the last 24 tokens of each one by one,
+    together in a batch.  In bfloat16 the prompt runs the tensor-memory attention over many
+    pages and query tiles, and decoding merges several key splits per request, a different
+    number for each."""
+    import sonicboom_b200 as sb
+    from conftest import INIT
+    sb.write_random_model(tmp_path, dict(TINY["B"], max_position_embeddings=2048), seed=21, **INIT["B"])
+    cfg, tensors = pm.read_model_dir(tmp_path)
+    eng = engine_for({"B": tmp_path}, "B", dtype)
+    reqs = prompts_for("B", [1800, 700], seed=6)
+    got = batch_unequal(eng, reqs, [len(r) - 24 for r in reqs])
+    for r, g in zip(reqs, got):
+        ref = pm.forward(cfg, tensors, r)
+        per_pos = (g - ref).abs().amax(dim=1) / ref.abs().max()
+        assert float(per_pos.max()) < TOL[dtype], f"{len(r)}: worst position {int(per_pos.argmax())}"
+    from sonicboom_b200 import ops
+    assert ops.tc5_status() == 0 and ops.attention_status(TINY["B"]["head_dim"]) == 0
+
+
 @pytest.mark.parametrize("name,dtype", CASES)
 def test_first_tokens_of_a_sequence(model_dirs, oracles, name, dtype):
     eng = engine_for(model_dirs, name, dtype)

@@ -352,6 +352,25 @@ def test_prefill_continues_a_sequence_on_the_tensor_memory_kernel():
     assert ops.attention_status(hd) == 0
 
 
+@pytest.mark.parametrize("hq,hkv,hd,window", [(28, 4, 128, 0), (28, 4, 128, 300), (16, 8, 64, 0), (2, 1, 256, 0)])
+def test_decode_steps_after_a_long_prompt(hq, hkv, hd, window):
+    """Head sizes and groups of the benchmark model (and two others): a prompt of several
+    splits, then single-token steps of two sequences of different lengths in one batch; every
+    step against the plain implementation on the whole sequence."""
+    cache = make_cache(hkv, hd, window, torch.bfloat16, max_tokens=2048)
+    lens = [777, 130]
+    xs = [torch.randn(n + 4, (hq + 2 * hkv) * hd, generator=torch.Generator().manual_seed(n)) for n in lens]
+    slots = [cache.open() for _ in lens]
+    run_attention(cache, hq, hkv, hd, window, torch.bfloat16, [(s, x[:n]) for s, x, n in zip(slots, xs, lens)])
+    for step in range(4):
+        out, _ = run_attention(cache, hq, hkv, hd, window, torch.bfloat16,
+                               [(s, x[n + step:n + step + 1]) for s, x, n in zip(slots, xs, lens)])
+        for i, (x, n) in enumerate(zip(xs, lens)):
+            ref = attention_ref(x[n + step:n + step + 1], n + step, hq, hkv, hd, window, history=x[:n + step])
+            close(out[i:i + 1], ref, 1.5e-2)
+    assert ops.attention_status(hd) == 0
+
+
 def test_a_far_key_is_found_by_the_tensor_memory_kernel():
     hq, hkv, hd, n = 8, 2, 64, 900
     for key_pos in (3, 64, 255, 511, 640, 895):
