@@ -222,10 +222,13 @@ __global__ void __launch_bounds__(PREFILL_THREADS) attn_prefill_kernel(const Att
   sb_pdl_launch();
   sb_pdl_wait();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int b = blockIdx.z, kvh = blockIdx.y;
+  // blockIdx.x = (block of query rows, key/value head), heads fastest and the last rows first:
+  // blocks are handed out in this order, so the longest ones of every head start first
+  const int b = blockIdx.z, kvh = blockIdx.x % p.n_kv_heads;
   const int G = p.n_q_heads / p.n_kv_heads;
   const int row0 = p.seq_row0[b], n_new = p.seq_row0[b + 1] - row0, pos0 = p.seq_pos0[b];
-  const int R = n_new * G, r_base = blockIdx.x * BM;
+  const int R = n_new * G;
+  const int r_base = (int)(gridDim.x / p.n_kv_heads - 1 - blockIdx.x / p.n_kv_heads) * BM;
   if (r_base >= R) return;
   const int32_t* pages = p.page_ids + p.page_off[b];
 
@@ -649,8 +652,8 @@ extern "C" int sb_attention(const void* q, void* out, int n_rows, int n_seqs, in
     if (!t5_make_map(&map_kv, cache, cache_rows))
       SB_FAIL(SB_ERR_CUDA, "sb_attention: cuTensorMapEncodeTiled failed");
     const long tiles5 = ((long)max_new * G + T5_QT * T5_ROWS - 1) / (T5_QT * T5_ROWS);
-    if (tiles5 > 2147483647L) SB_FAIL(SB_ERR_UNSUPPORTED, "sb_attention: too many rows");
-    sb_launch<SB_K_ATTENTION>(attn_prefill_tc5_kernel, dim3((unsigned)tiles5, n_kv_heads, n_seqs),
+    if (tiles5 * n_kv_heads > 2147483647L) SB_FAIL(SB_ERR_UNSUPPORTED, "sb_attention: too many rows");
+    sb_launch<SB_K_ATTENTION>(attn_prefill_tc5_kernel, dim3((unsigned)(tiles5 * n_kv_heads), 1, n_seqs),
               dim3(T5_THREADS), T5_SMEM, stream, map_kv, p);
     SB_CHECK_LAUNCH("sb_attention (prefill, tcgen05)");
     if (tc5_checked) return SB_OK;
@@ -670,9 +673,9 @@ extern "C" int sb_attention(const void* q, void* out, int n_rows, int n_seqs, in
   }
 #endif
   const long tiles = ((long)max_new * G + BM - 1) / BM;
-  if (tiles > 2147483647L) SB_FAIL(SB_ERR_UNSUPPORTED, "sb_attention: too many rows");
-  sb_launch<SB_K_ATTENTION>(attn_prefill_kernel, dim3((unsigned)tiles, n_kv_heads, n_seqs), dim3(PREFILL_THREADS), PREFILL_SMEM,
-            stream, p);
+  if (tiles * n_kv_heads > 2147483647L) SB_FAIL(SB_ERR_UNSUPPORTED, "sb_attention: too many rows");
+  sb_launch<SB_K_ATTENTION>(attn_prefill_kernel, dim3((unsigned)(tiles * n_kv_heads), 1, n_seqs),
+                            dim3(PREFILL_THREADS), PREFILL_SMEM, stream, p);
   SB_CHECK_LAUNCH("sb_attention (prefill)");
   return SB_OK;
 }

@@ -124,11 +124,13 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_kv, const AttnPa
   sb_pdl_launch();
   sb_pdl_wait();
 
-  const int b = blockIdx.z, kvh = blockIdx.y;
+  // blockIdx.x = (block of query rows, key/value head), heads fastest and the last rows first:
+  // blocks are handed out in this order, so the longest ones of every head start first
+  const int b = blockIdx.z, kvh = blockIdx.x % p.n_kv_heads;
   const int G = p.n_q_heads / p.n_kv_heads;
   const int row0 = p.seq_row0[b], n_new = p.seq_row0[b + 1] - row0, pos0 = p.seq_pos0[b];
   const int R = n_new * G;
-  const int r_base = (int)(gridDim.x - 1 - blockIdx.x) * (T5_QT * T5_ROWS);   // long rows first
+  const int r_base = (int)(gridDim.x / p.n_kv_heads - 1 - blockIdx.x / p.n_kv_heads) * (T5_QT * T5_ROWS);
   if (r_base >= R) return;
   const int r_last = min(R, r_base + T5_QT * T5_ROWS) - 1;
   const int tile_lo = (p.window > 0 ? max(0, pos0 + r_base / G - p.window + 1) : 0) / KT;
