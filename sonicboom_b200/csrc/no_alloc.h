@@ -6,7 +6,7 @@
 // real-time loop, a callback of another framework that owns the allocator, a process whose
 // memory budget was handed out in full at start-up).  The ordinary entry point, sb_attention,
 // asks its caller for scratch memory whenever a sequence is long enough to be cut into more
-// than one split of 256 keys; such a caller has nowhere to get it from.
+// than one split (256 keys, 512 in long sequences); such a caller has nowhere to get it from.
 //
 // Here the scratch is a fixed array inside the library's own device image
 // (SB_STATIC_SCRATCH_BYTES, 8 MiB per GPU that loads the library, held until the process

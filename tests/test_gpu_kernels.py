@@ -371,6 +371,30 @@ def test_decode_steps_after_a_long_prompt(hq, hkv, hd, window):
     assert ops.attention_status(hd) in (0, -1)            # -1: no tensor-memory kernel at this head size
 
 
+def test_decode_attention_across_the_split_length_change():
+    """Splits are 256 keys up to a sequence length of 4,096 and 512 beyond.  A sequence that
+    grows from 4,094 to 4,099 keys crosses the change, next to a short one in the same batch;
+    every step against the plain implementation, and the far key at position 3 is still found."""
+    hq, hkv, hd = 4, 1, 64
+    cache = make_cache(hkv, hd, 0, torch.bfloat16, max_tokens=4096 + 256 + 128)
+    lens = [4093, 200]
+    xs = [torch.randn(n + 6, (hq + 2 * hkv) * hd, generator=torch.Generator().manual_seed(n)) for n in lens]
+    slots = [cache.open() for _ in lens]
+    run_attention(cache, hq, hkv, hd, 0, torch.bfloat16, [(s, x[:n]) for s, x, n in zip(slots, xs, lens)])
+    for step in range(6):
+        out, _ = run_attention(cache, hq, hkv, hd, 0, torch.bfloat16,
+                               [(s, x[n + step:n + step + 1]) for s, x, n in zip(slots, xs, lens)])
+        for i, (x, n) in enumerate(zip(xs, lens)):
+            ref = attention_ref(x[n + step:n + step + 1], n + step, hq, hkv, hd, 0, history=x[:n + step])
+            close(out[i:i + 1], ref, 1.5e-2)
+    cache2 = make_cache(hkv, hd, 0, torch.bfloat16, max_tokens=4096 + 256)
+    x = standout(4200, hq, hkv, hd, 3)
+    s = cache2.open()
+    run_attention(cache2, hq, hkv, hd, 0, torch.bfloat16, [(s, x[:4199])], rot=0)
+    out, _ = run_attention(cache2, hq, hkv, hd, 0, torch.bfloat16, [(s, x[4199:])], rot=0)
+    assert abs(float(out.mean()) - 4.0) < 0.08, float(out.mean())
+
+
 def test_a_far_key_is_found_by_the_tensor_memory_kernel():
     hq, hkv, hd, n = 8, 2, 64, 900
     for key_pos in (3, 64, 255, 511, 640, 895):
