@@ -17,6 +17,8 @@
 //
 // Every wait on an mbarrier is bounded; when a bound is hit the kernel records a code in a
 // status word, stops issuing work and leaves normally (sb_tc5_status reads the word).
+#include <cooperative_groups.h>
+
 #include "tc5.cuh"
 
 int sb_check_linear_args(const char* who, int M, int N, int K, int epilogue, const void* bias,
@@ -446,6 +448,112 @@ tc5_reduce_kernel(const Tc5Params p, int bn) {
   }
 }
 
+// The same sum for a row-wise epilogue, followed by the RMSNorm of the finished rows: what a
+// pre-norm block's next product reads.  A cluster of RN_CLUSTER blocks takes one token; a block
+// adds the partial tiles of its part of the row, writes the float32 result, and the blocks
+// exchange their sums of squares through each other's shared memory, so that the row is neither
+// written and read again for the norm nor waits for another launch.  The sum of squares is added
+// in a fixed order (threads, warps, blocks), so the result does not depend on timing.
+constexpr int RN_CLUSTER = 4, RN_THREADS = 256, RN_VEC = 4;
+constexpr int RN_MAX_WIDTH = RN_CLUSTER * RN_THREADS * RN_VEC * 4;
+
+__device__ __forceinline__ void rn_load4(const float* p, float (&v)[4]) {
+  const float4 f = *reinterpret_cast<const float4*>(p);
+  v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+}
+__device__ __forceinline__ void rn_load4(const bf16* p, float (&v)[4]) {
+  const uint2 u = *reinterpret_cast<const uint2*>(p);
+  const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&u.x);
+  const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&u.y);
+  v[0] = __low2float(a); v[1] = __high2float(a); v[2] = __low2float(b); v[3] = __high2float(b);
+}
+__device__ __forceinline__ void rn_store4(float* p, const float (&v)[4]) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+__device__ __forceinline__ void rn_store4(bf16* p, const float (&v)[4]) {
+  __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+  uint2 u;
+  u.x = *reinterpret_cast<uint32_t*>(&a);
+  u.y = *reinterpret_cast<uint32_t*>(&b);
+  *reinterpret_cast<uint2*>(p) = u;
+}
+
+template <typename TW, typename TN>
+__global__ void __launch_bounds__(RN_THREADS)
+tc5_reduce_norm_kernel(const Tc5Params p, int bn, const TW* __restrict__ norm_w, float eps,
+                       TN* __restrict__ norm_out) {
+  namespace cg = cooperative_groups;
+  cg::cluster_group cluster = cg::this_cluster();
+  __shared__ float warp_sums[RN_THREADS / 32];
+  __shared__ float block_sums[RN_CLUSTER];          // slot c is written by block c of the cluster
+  sb_pdl_launch();
+  const int j = blockIdx.y;                                             // token
+  const int c = (int)cluster.block_rank();
+  const int groups = p.N / 4, per = (groups + RN_CLUSTER - 1) / RN_CLUSTER;
+  const int g0 = c * per, g1 = min(groups, g0 + per);
+  float wv[RN_VEC][4];
+#pragma unroll
+  for (int i = 0; i < RN_VEC; ++i) {                 // the norm's weights wait for nobody
+    const int g = g0 + threadIdx.x + i * RN_THREADS;
+    if (g < g1) rn_load4(norm_w + (size_t)g * 4, wv[i]);
+  }
+  sb_pdl_wait();
+  float v[RN_VEC][4];
+  float sq = 0.0f;
+#pragma unroll
+  for (int i = 0; i < RN_VEC; ++i) {
+    const int g = g0 + threadIdx.x + i * RN_THREADS;
+    if (g >= g1) continue;
+    const int e = g * 4, tile = e / BM, f = e % BM;
+    const float* base = p.scratch + (((size_t)tile * p.k_splits) * bn + j) * BM + f;
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    for (int s = 0; s < p.k_splits; ++s) {
+      const float4 t = *reinterpret_cast<const float4*>(base + (size_t)s * bn * BM);
+      acc[0] += t.x; acc[1] += t.y; acc[2] += t.z; acc[3] += t.w;
+    }
+    if (p.epilogue == SB_EPI_BIAS) {
+      float b[4];
+      if (p.bias_dtype == SB_F32) rn_load4((const float*)p.bias + e, b);
+      else rn_load4((const bf16*)p.bias + e, b);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) acc[k] += b[k];
+    } else if (p.epilogue == SB_EPI_RESIDUAL) {
+      float r[4];
+      rn_load4(p.residual + (size_t)j * p.N + e, r);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) acc[k] += r[k];
+    }
+    rn_store4((float*)p.out + (size_t)j * p.N + e, acc);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      v[i][k] = acc[k];
+      sq = fmaf(acc[k], acc[k], sq);
+    }
+  }
+  sq = sb_warp_sum(sq);
+  if ((threadIdx.x & 31) == 0) warp_sums[threadIdx.x >> 5] = sq;
+  __syncthreads();
+  if (threadIdx.x < RN_CLUSTER) {                    // thread t tells block t of the cluster
+    float total = 0.0f;
+    for (int i = 0; i < RN_THREADS / 32; ++i) total += warp_sums[i];
+    *cluster.map_shared_rank(&block_sums[c], threadIdx.x) = total;
+  }
+  cluster.sync();                                    // after it nobody touches another block's memory
+  float total = 0.0f;
+#pragma unroll
+  for (int i = 0; i < RN_CLUSTER; ++i) total += block_sums[i];
+  const float inv = 1.0f / sqrtf(total / (float)p.N + eps);
+#pragma unroll
+  for (int i = 0; i < RN_VEC; ++i) {
+    const int g = g0 + threadIdx.x + i * RN_THREADS;
+    if (g >= g1) continue;
+    float y[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) y[k] = (v[i][k] * inv) * wv[i][k];
+    rn_store4(norm_out + (size_t)j * p.N + (size_t)g * 4, y);
+  }
+}
+
 // --------------------------------------------------------------------------- host side
 // A [rows, K] bfloat16 row-major matrix as a tensor map with boxes of box_rows x 64.
 bool make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) {
@@ -543,12 +651,56 @@ extern "C" size_t sb_gemm_tc5_scratch_bytes(int M, int N, int K, int n_sms) {
   return (size_t)tiles * splits * swapped_bn(M) * BM * sizeof(float);
 }
 
-extern "C" int sb_gemm_tc5(const void* A, int a_dtype, const void* W, int w_dtype, int M, int N,
-                           int K, int epilogue, const void* bias, int bias_dtype,
-                           const float* residual, void* out, int out_dtype, void* scratch,
-                           size_t scratch_bytes, int n_sms, int form, cudaStream_t stream) {
+// An RMSNorm of the product's rows, asked for together with the product.
+struct NormRequest {
+  const void* weight;
+  int weight_dtype;
+  float eps;
+  void* out;
+  int out_dtype;
+};
+
+extern "C" int sb_rmsnorm(const float* x, const int32_t* rows, int n_rows, int width,
+                          const void* weight, int weight_dtype, float eps, void* out,
+                          int out_dtype, cudaStream_t stream);
+
+// Whether the swapped split-K form can finish these rows with the fused reduce + norm kernel.
+static bool norm_fuses(int M, int N, int K, int n_sms, int epilogue, int out_dtype, int form) {
+  const bool normal = form == 1 || (form == 0 && M > 64);
+  return !normal && M <= 64 && choose_splits(N, K, n_sms) > 1 && epilogue != SB_EPI_SWIGLU &&
+         out_dtype == SB_F32 && N % 4 == 0 && N <= RN_MAX_WIDTH;
+}
+
+extern "C" int sb_gemm_tc5_fuses_norm(int M, int N, int K, int n_sms, int epilogue, int out_dtype,
+                                      int form) {
+  return norm_fuses(M, N, K, n_sms, epilogue, out_dtype, form) ? 1 : 0;
+}
+
+static int tc5_run(const void* A, int a_dtype, const void* W, int w_dtype, int M, int N,
+                   int K, int epilogue, const void* bias, int bias_dtype,
+                   const float* residual, void* out, int out_dtype, void* scratch,
+                   size_t scratch_bytes, int n_sms, int form, const NormRequest* norm,
+                   cudaStream_t stream) {
   if (int rc = sb_check_linear_args("sb_gemm_tc5", M, N, K, epilogue, bias, residual, out_dtype))
     return rc;
+  if (norm) {
+    if (epilogue == SB_EPI_SWIGLU || out_dtype != SB_F32)
+      SB_FAIL(SB_ERR_UNSUPPORTED, "sb_gemm_tc5: a norm follows a float32 product without SwiGLU");
+    if (!norm->weight || !norm->out || !sb_valid_dtype(norm->weight_dtype) ||
+        !sb_valid_dtype(norm->out_dtype) || !(norm->eps >= 0.0f))
+      SB_FAIL(SB_ERR_ARG, "sb_gemm_tc5: norm weight, output, dtype codes %d %d or eps %g",
+              norm->weight_dtype, norm->out_dtype, norm->eps);
+    if (!norm_fuses(M, N, K, n_sms, epilogue, out_dtype, form) ||
+        (((uintptr_t)norm->weight | (uintptr_t)norm->out | (uintptr_t)out | (uintptr_t)residual |
+          (uintptr_t)bias) & 15)) {
+      // the product as usual, then the norm as a kernel of its own
+      if (int rc = tc5_run(A, a_dtype, W, w_dtype, M, N, K, epilogue, bias, bias_dtype, residual,
+                           out, out_dtype, scratch, scratch_bytes, n_sms, form, nullptr, stream))
+        return rc;
+      return sb_rmsnorm((const float*)out, nullptr, M, N, norm->weight, norm->weight_dtype,
+                        norm->eps, norm->out, norm->out_dtype, stream);
+    }
+  }
   if (a_dtype != SB_BF16 || w_dtype != SB_BF16)
     SB_FAIL(SB_ERR_UNSUPPORTED, "sb_gemm_tc5: takes bfloat16 operands (got dtype codes %d, %d)",
             a_dtype, w_dtype);
@@ -619,6 +771,29 @@ extern "C" int sb_gemm_tc5(const void* A, int a_dtype, const void* W, int w_dtyp
   else { SB_TC5_SWAPPED(64, 4) }
 #undef SB_TC5_SWAPPED
   if (rc != SB_OK || splits <= 1) return rc;
+  if (norm) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(RN_CLUSTER, (unsigned)M);
+    cfg.blockDim = dim3(RN_THREADS);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = RN_CLUSTER;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = (sb_pdl_enabled() & SB_K_REDUCE) ? 2 : 1;
+    SB_DISPATCH_DTYPE(norm->weight_dtype, TW, {
+      SB_DISPATCH_DTYPE(norm->out_dtype, TN, {
+        cudaLaunchKernelEx(&cfg, tc5_reduce_norm_kernel<TW, TN>, p, bn, (const TW*)norm->weight,
+                           norm->eps, (TN*)norm->out);
+      });
+    });
+    SB_CHECK_LAUNCH("sb_gemm_tc5 (reduce + norm)");
+    return SB_OK;
+  }
   const int n_out = epilogue == SB_EPI_SWIGLU ? N / 2 : N;
   const long work = (long)((n_out + 3) / 4) * M;
   const dim3 rgrid((unsigned)((work + 255) / 256));
@@ -626,4 +801,25 @@ extern "C" int sb_gemm_tc5(const void* A, int a_dtype, const void* W, int w_dtyp
   else sb_launch<SB_K_REDUCE>(tc5_reduce_kernel<bf16>, rgrid, dim3(256), 0, stream, p, bn);
   SB_CHECK_LAUNCH("sb_gemm_tc5 (reduce)");
   return SB_OK;
+}
+
+extern "C" int sb_gemm_tc5(const void* A, int a_dtype, const void* W, int w_dtype, int M, int N,
+                           int K, int epilogue, const void* bias, int bias_dtype,
+                           const float* residual, void* out, int out_dtype, void* scratch,
+                           size_t scratch_bytes, int n_sms, int form, cudaStream_t stream) {
+  return tc5_run(A, a_dtype, W, w_dtype, M, N, K, epilogue, bias, bias_dtype, residual, out,
+                 out_dtype, scratch, scratch_bytes, n_sms, form, nullptr, stream);
+}
+
+// The product, and norm_out = RMSNorm(out) * norm_weight over the rows of the float32 result:
+// one kernel with the split-K sum where that form runs, else a norm kernel after the product.
+extern "C" int sb_gemm_tc5_norm(const void* A, int a_dtype, const void* W, int w_dtype, int M,
+                                int N, int K, int epilogue, const void* bias, int bias_dtype,
+                                const float* residual, void* out, int out_dtype, void* scratch,
+                                size_t scratch_bytes, int n_sms, int form, const void* norm_weight,
+                                int norm_weight_dtype, float norm_eps, void* norm_out,
+                                int norm_out_dtype, cudaStream_t stream) {
+  const NormRequest norm = {norm_weight, norm_weight_dtype, norm_eps, norm_out, norm_out_dtype};
+  return tc5_run(A, a_dtype, W, w_dtype, M, N, K, epilogue, bias, bias_dtype, residual, out,
+                 out_dtype, scratch, scratch_bytes, n_sms, form, &norm, stream);
 }

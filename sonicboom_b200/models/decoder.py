@@ -78,6 +78,9 @@ class DecoderModel:
             ctx.entry = i
             ctx.owns_cache = e.cache_from is None
             ctx.kv_entry = i if e.cache_from is None else e.cache_from
+            # the next entry's first norm can ride on this entry's last product
+            ctx.after_block_norm = self.blocks[s.schedule[i + 1].layer].input_norm() \
+                if i + 1 < len(s.schedule) else None
             x = self.blocks[e.layer].forward(x, ctx)
         if plan.n_want == 0:
             return None

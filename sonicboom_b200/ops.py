@@ -108,8 +108,12 @@ def cast(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
 
 def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = EPI_NONE,
            bias: torch.Tensor | None = None, residual: torch.Tensor | None = None,
-           kernel: str = "auto") -> torch.Tensor:
+           kernel: str = "auto", norm: tuple | None = None) -> torch.Tensor:
     """out = a @ w.T with a fused epilogue; a [M,K], w [N,K]; float32 accumulation.
+
+    `norm` = (weight, eps, norm_out) also writes norm_out = rmsnorm(out, weight, eps) [M,N]
+    (out must be float32): in the kernel that finishes the product where one does (the split-K
+    decode form of the tcgen05 kernel), else with the norm kernel after it.
 
     bfloat16 operands run on tensor cores: `kernel` "tc5" (TMA + tcgen05), "skinny" (weights
     streamed into mma.sync fragments, at most SKINNY_MAX_ROWS rows), "tiled" (mma.sync tiles),
@@ -136,6 +140,22 @@ def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = 
         assert bias.numel() == N
     fast = a.dtype == torch.bfloat16 and kernel != "plain" and K % 8 == 0
     l = lib()
+    if norm is not None:
+        norm_w, norm_eps, norm_out = norm
+        assert out.dtype == torch.float32 and epilogue != EPI_SWIGLU
+        assert norm_w.numel() == N and tuple(norm_out.shape) == (M, N)
+        fuses = fast and kernel in ("auto", "tc5") and bool(l.sb_gemm_tc5_fuses_norm(
+            M, N, K, _sm_count(a.device), epilogue, _code(out.dtype), 0))
+        if fuses and (kernel == "tc5" or FORCE_DECODE_KERNEL != "skinny"):
+            ws = _tc5_workspace(M, N, K, a.device)
+            _check(l.sb_gemm_tc5_norm(
+                *args[:-1], _ptr(ws), ctypes.c_size_t(ws.numel()), _sm_count(a.device), 0,
+                _ptr(norm_w), _code(norm_w.dtype), ctypes.c_float(norm_eps), _ptr(norm_out),
+                _code(norm_out.dtype), _stream()), "linear (tcgen05 kernel with norm)", launches=2)
+            return out
+        linear(a, w, out, epilogue, bias, residual, kernel)
+        rmsnorm(out, norm_w, norm_eps, norm_out)
+        return out
     if kernel == "auto" and fast:
         kernel = _pick_kernel(M, N, K, a.device)
     if fast and kernel in ("tc5", "tc5_normal"):

@@ -74,9 +74,9 @@ class Attention(Mixer):
                       self.spec.window, self.spec.scale)
         out = residual if residual is not None else \
             torch.empty((rows, self.spec.width), dtype=torch.float32, device=h.device)
-        return ops.linear(mixed, self.w_o, out,
+        return ctx.linear(mixed, self.w_o, out,
                           ops.EPI_RESIDUAL if residual is not None else ops.EPI_NONE,
-                          residual=residual)
+                          residual=residual, act_dtype=self.dtype)
 
 
 def _cat(tensors):

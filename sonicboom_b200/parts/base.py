@@ -12,6 +12,14 @@ Every part follows the same life cycle:
 
 What a step hands to parts is a `StepContext`: the step's device-side plan (rows, positions,
 page tables), the cache, and which schedule entry is running.
+
+A norm that directly follows a part's last product can be computed by the kernel that finishes
+the product.  Whoever will apply the norm names it in `ctx.next_norm` before it calls the part;
+a part that ends in a product calls `ctx.linear(...)` instead of `ops.linear(...)`, which hands
+the normed rows back through `ctx.take_normed(norm, rows)`.  Across blocks the model names the
+next entry's first norm in `ctx.after_block_norm`, and a block whose result is its last part's
+result passes it on as that part's `next_norm`.  Parts and blocks that ignore all this are still
+right: `take_normed` then returns None and the caller runs the norm itself.
 """
 from __future__ import annotations
 
@@ -20,6 +28,7 @@ from typing import Callable, Optional
 
 import torch
 
+from .. import ops
 from ..cache.kv import Cache, KVNeed, StateNeed
 from ..weights.loader import TensorRequest
 
@@ -31,6 +40,27 @@ class StepContext:
     entry: int = 0                 # index of the running schedule entry
     kv_entry: int = 0              # entry whose cache is read (== entry when it owns one)
     owns_cache: bool = True
+    next_norm: Optional["Norm"] = None     # the norm the caller applies to the running part's result
+    after_block_norm: Optional["Norm"] = None   # the first norm of the entry that runs next (for blocks)
+    _normed: Optional[tuple] = None        # (norm, rows, normed rows) of the last `linear` that had one
+
+    def linear(self, a, w, out, epilogue, residual=None, bias=None, act_dtype=None):
+        """ops.linear into float32 `out`; when `next_norm` is an RMS norm with a plain weight,
+        its result over the finished rows (in `act_dtype`) is produced with it and kept for
+        `take_normed`."""
+        norm, self.next_norm, self._normed = self.next_norm, None, None
+        rms = norm.as_rms() if norm is not None else None
+        if rms is None or out.dtype != torch.float32 or epilogue == ops.EPI_SWIGLU:
+            return ops.linear(a, w, out, epilogue, bias=bias, residual=residual)
+        normed = torch.empty(out.shape, dtype=act_dtype or a.dtype, device=out.device)
+        ops.linear(a, w, out, epilogue, bias=bias, residual=residual, norm=(rms[0], rms[1], normed))
+        self._normed = (norm, out, normed)
+        return out
+
+    def take_normed(self, norm, x) -> Optional[torch.Tensor]:
+        """`norm` of the rows `x`, if the part that just ran left it behind; else None."""
+        kept, self._normed, self.next_norm = self._normed, None, None
+        return kept[2] if kept is not None and kept[0] is norm and kept[1] is x else None
 
     def kv_storage(self) -> torch.Tensor:
         """[page, k|v, kv head, position in page, hd] of the cache this entry reads."""
@@ -59,6 +89,11 @@ class Norm(Part):
 
     def forward(self, x, out_dtype, rows=None):
         raise NotImplementedError
+
+    def as_rms(self) -> Optional[tuple]:
+        """(weight, eps) when the norm is y = x / sqrt(mean(x^2) + eps) * weight, else None:
+        what a product kernel needs to apply it to its own result."""
+        return None
 
 
 class PositionEncoding(Part):
@@ -94,6 +129,11 @@ class Block(Part):
 
     def forward(self, x, ctx: StepContext):
         raise NotImplementedError
+
+    def input_norm(self) -> Optional[Norm]:
+        """The norm this arrangement applies to its input first, if it starts with one: the
+        entry before it may then deliver the normed rows (see `StepContext.take_normed`)."""
+        return None
 
     def kv_need(self):
         return None

@@ -29,7 +29,17 @@ class PreNormBlock(Block):
     def state_need(self):
         return self.mixer.state_need()
 
+    def input_norm(self):
+        return self.mixer_norm
+
     def forward(self, x, ctx):
-        x = self.mixer.forward(self.mixer_norm.forward(x, self.dtype), ctx, residual=x)
-        return self.feed_forward.forward(self.feed_forward_norm.forward(x, self.dtype), ctx,
-                                         residual=x)
+        h = ctx.take_normed(self.mixer_norm, x)
+        if h is None:
+            h = self.mixer_norm.forward(x, self.dtype)
+        ctx.next_norm = self.feed_forward_norm
+        x = self.mixer.forward(h, ctx, residual=x)
+        f = ctx.take_normed(self.feed_forward_norm, x)
+        if f is None:
+            f = self.feed_forward_norm.forward(x, self.dtype)
+        ctx.next_norm = ctx.after_block_norm       # the block's result is the feed-forward's
+        return self.feed_forward.forward(f, ctx, residual=x)

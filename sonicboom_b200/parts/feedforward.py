@@ -53,6 +53,6 @@ class SwiGLU(FeedForward):
         ops.linear(h, self.w_gate_up, t, ops.EPI_SWIGLU)
         out = residual if residual is not None else \
             torch.empty((rows, self.spec.width), dtype=torch.float32, device=h.device)
-        return ops.linear(t, self.w_down, out,
+        return ctx.linear(t, self.w_down, out,
                           ops.EPI_RESIDUAL if residual is not None else ops.EPI_NONE,
-                          residual=residual)
+                          residual=residual, act_dtype=self.dtype)

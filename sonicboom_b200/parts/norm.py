@@ -21,6 +21,9 @@ class RMSNorm(Norm):
     def bind(self, get):
         self.weight = get(self.tensor)
 
+    def as_rms(self):
+        return self.weight, self.eps
+
     def forward(self, x, out_dtype, rows=None):
         n = x.shape[0] if rows is None else rows.numel()
         out = torch.empty((n, self.width), dtype=out_dtype, device=x.device)

@@ -128,6 +128,42 @@ def test_linear_rows_do_not_depend_on_the_batch(kernel):
         assert pm.rel_err(part.cpu(), full[rows].cpu()) < 1e-6
 
 
+def rmsnorm_ref(x, w, eps):
+    x = x.double().cpu()
+    return (x / torch.sqrt((x * x).mean(dim=1, keepdim=True) + eps) * w.double().cpu()).float()
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 1000, 512), (8, 3584, 1024), (13, 520, 2048), (33, 2052, 328),
+                                   (64, 896, 4864), (8, 16388, 512), (8, 250, 512), (70, 512, 512)])
+@pytest.mark.parametrize("ndtype", ["float32", "bfloat16"])
+def test_linear_followed_by_a_norm(M, N, K, ndtype):
+    """A product with the norm of its rows asked for: through the kernel that finishes the
+    split-K product where it runs (up to 64 rows, widths that are multiples of 4 up to 16,384),
+    else product then norm.  The product itself is the same to the bit either way."""
+    a = rnd(M, K, dtype=torch.bfloat16)
+    w = rnd(N, K, dtype=torch.bfloat16, scale=K ** -0.5, seed=1)
+    bias, res = rnd(N, dtype=torch.bfloat16, seed=2), rnd(M, N, seed=3)
+    nw = (1 + 0.3 * rnd(N, seed=4)).to(DT[ndtype])
+    eps = 3e-5
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    for epi in (ops.EPI_NONE, ops.EPI_BIAS, ops.EPI_RESIDUAL):
+        kw = dict(bias=bias if epi == ops.EPI_BIAS else None)
+        plain_out = torch.empty(M, N, device=DEV)
+        ops.linear(a, w, plain_out, epi, residual=res.clone() if epi == ops.EPI_RESIDUAL else None,
+                   kernel="tc5", **kw)
+        out = res.clone() if epi == ops.EPI_RESIDUAL else torch.empty(M, N, device=DEV)
+        normed = torch.empty(M, N, dtype=DT[ndtype], device=DEV)
+        ops.linear(a, w, out, epi, residual=out if epi == ops.EPI_RESIDUAL else None,
+                   norm=(nw, eps, normed), **kw)
+        fuses = bool(ops.lib().sb_gemm_tc5_fuses_norm(M, N, K, sms, epi, 0, 0))
+        assert fuses == (M <= 64 and N % 4 == 0 and N <= 16384 and K >= 512)   # K split at 8 tiles of 64
+        if fuses:
+            assert torch.equal(out, plain_out)
+        close(out, linear_ref(a, w, epi, bias, res), 1e-5)
+        close(normed, rmsnorm_ref(out, nw, eps), 1e-6 if ndtype == "float32" else 5e-3)   # bfloat16: half an ulp is 2^-8
+    assert ops.tc5_status() == 0
+
+
 def test_fused_gate_up_layout():
     gate, up = rnd(32, 8), rnd(32, 8, seed=1)
     f = interleave_gate_up(gate, up)
