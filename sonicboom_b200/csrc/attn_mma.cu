@@ -66,6 +66,8 @@ struct AttnParams {
   int n_q_heads, n_kv_heads, window, n_splits;
   int n_seqs;
   float scale_log2;            // scale * log2(e)
+  const char* warm;            // decode: bytes the next kernel will read, asked into L2 (or null)
+  size_t warm_bytes;
 };
 
 __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0,
@@ -392,6 +394,11 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(const AttnP
     cp_async_commit();
   }
   sb_pdl_launch();                                    // the keys and values have been read
+  if (p.warm_bytes && tid == 0)
+    // what is left of this kernel (the merges) reads little: every block asks for its share
+    // of the bytes the next kernel will stream
+    sb_warm_l2(p.warm, p.warm_bytes, ((size_t)blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x,
+               (size_t)gridDim.x * gridDim.y * gridDim.z);
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
     l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
@@ -597,7 +604,7 @@ extern "C" int sb_attention(const void* q, void* out, int n_rows, int n_seqs, in
                             const void* cache, int n_q_heads, int n_kv_heads, int hd, int window,
                             float scale, void* scratch, size_t scratch_bytes, int* counters,
                             int n_counters, int max_len, int n_pages, int n_sms,
-                            cudaStream_t stream) {
+                            const void* warm, size_t warm_bytes, cudaStream_t stream) {
   if (hd != HD) SB_FAIL(SB_ERR_ARG, "sb_attention: built for head size %d, called with %d", HD, hd);
   if (page_size != KT)
     SB_FAIL(SB_ERR_UNSUPPORTED, "sb_attention: cache pages of %d keys (needs %d)", page_size, KT);
@@ -612,6 +619,7 @@ extern "C" int sb_attention(const void* q, void* out, int n_rows, int n_seqs, in
   if ((((uintptr_t)q | (uintptr_t)cache | (uintptr_t)scratch) & 15) || ((uintptr_t)out & 7))
     SB_FAIL(SB_ERR_ARG, "sb_attention: unaligned operands");
   AttnParams p;
+  p.warm = (const char*)warm; p.warm_bytes = sb_warm_bytes(warm, warm_bytes);
   p.q = (const bf16*)q; p.out = (bf16*)out;
   p.seq_row0 = seq_row0; p.seq_pos0 = seq_pos0; p.page_off = page_off; p.page_ids = page_ids;
   p.cache = (const bf16*)cache; p.scratch = (float*)scratch; p.counters = counters;
@@ -770,6 +778,7 @@ extern "C" int sb_attention_decode_static(const void* q, void* out, int n_rows, 
   }
 
   AttnParams p;
+  p.warm = nullptr; p.warm_bytes = 0;
   p.q = (const bf16*)q; p.out = (bf16*)out;
   p.seq_row0 = seq_row0; p.seq_pos0 = seq_pos0; p.page_off = page_off; p.page_ids = page_ids;
   p.cache = (const bf16*)cache; p.scratch = g_static_scratch_ptr[device];

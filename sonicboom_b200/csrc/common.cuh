@@ -78,6 +78,35 @@ __device__ __forceinline__ void sb_pdl_launch() {
   asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
 }
 
+// Asks for memory that a later kernel will stream (weights) to be brought into L2: a kernel
+// calls this once its own loads have landed, where the rest of it (a merge) leaves the memory
+// system idle and the next kernel's blocks cannot start yet.  (The tcgen05 products need no such
+// hint from the kernel before them: launched early, they request their first tiles themselves.)  Block `bid` of `n_blocks` asks for its share; `ptr` is 16-byte
+// aligned and `bytes` a multiple of 16.  A hint only: nothing waits for it.
+constexpr uint32_t SB_WARM_CHUNK = 16384;
+constexpr size_t SB_WARM_MAX = (size_t)32 << 20;
+__device__ __forceinline__ void sb_warm_l2(const char* ptr, size_t bytes, size_t bid, size_t n_blocks) {
+  for (size_t off = bid * SB_WARM_CHUNK; off < bytes; off += n_blocks * SB_WARM_CHUNK) {
+    const uint32_t n = (uint32_t)(bytes - off < SB_WARM_CHUNK ? bytes - off : SB_WARM_CHUNK);
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"(ptr + off), "r"(n) : "memory");
+  }
+}
+// The bytes of a hint as the kernels take them: nothing for an unaligned pointer, at most
+// SB_WARM_MAX (what the idle stretch of a decode kernel can bring in), a multiple of 16.
+static inline size_t sb_warm_bytes(const void* ptr, size_t bytes) {
+  if (!ptr || ((uintptr_t)ptr & 15)) return 0;
+  return (bytes < SB_WARM_MAX ? bytes : SB_WARM_MAX) & ~(size_t)15;
+}
+
+// What may accompany a product: the RMSNorm of its finished rows.
+struct SbLinearExtras {
+  const void* norm_weight;     // null: no norm
+  int norm_weight_dtype;
+  float norm_eps;
+  void* norm_out;
+  int norm_out_dtype;
+};
+
 // Kernel classes, as bits of the mask that says which kernels get the launch attribute.
 enum SbKernelClass {
   SB_K_TC5 = 1,          // tcgen05 products

@@ -10,23 +10,31 @@ extern "C" int sb_abi_version() { return 1; }
 // Inputs that an earlier kernel of the step wrote are plain pointers, not `const __restrict__`:
 // with programmatic dependent launch a kernel may start before its predecessor has finished, and
 // the non-coherent load path that `const __restrict__` selects could then return stale lines.
+// An id outside the table (the sampler's -1 for a row of logits that are not finite, when ids are
+// fed back on the device) reads nothing and gives a row of NaN, which stays visible downstream.
 template <typename TW>
-__global__ void embed_kernel(const int32_t* tokens, const TW* __restrict__ table,
+__global__ void embed_kernel(const int32_t* tokens, const TW* __restrict__ table, int vocab,
                              int width, float* __restrict__ out) {
   sb_pdl_launch();
   sb_pdl_wait();
   const int t = blockIdx.x;
-  const TW* row = table + (size_t)tokens[t] * width;
+  const int id = tokens[t];
   float* o = out + (size_t)t * width;
+  if ((unsigned)id >= (unsigned)vocab) {
+    for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = __int_as_float(0x7fc00000);
+    return;
+  }
+  const TW* row = table + (size_t)id * width;
   for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = sb_to_f32<TW>(row[i]);
 }
 
 extern "C" int sb_embed(const int32_t* tokens, int n_rows, const void* table, int table_dtype,
-                        int width, float* out, cudaStream_t stream) {
-  if (n_rows <= 0 || width <= 0) SB_FAIL(SB_ERR_ARG, "sb_embed: n_rows=%d width=%d", n_rows, width);
+                        int vocab, int width, float* out, cudaStream_t stream) {
+  if (n_rows <= 0 || width <= 0 || vocab <= 0)
+    SB_FAIL(SB_ERR_ARG, "sb_embed: n_rows=%d vocab=%d width=%d", n_rows, vocab, width);
   if (!sb_valid_dtype(table_dtype)) SB_FAIL(SB_ERR_ARG, "sb_embed: table dtype %d", table_dtype);
   SB_DISPATCH_DTYPE(table_dtype, TW, {
-    sb_launch<SB_K_ELEMENTWISE>(embed_kernel<TW>, dim3(n_rows), dim3(256), 0, stream, tokens, (const TW*)table, width, out);
+    sb_launch<SB_K_ELEMENTWISE>(embed_kernel<TW>, dim3(n_rows), dim3(256), 0, stream, tokens, (const TW*)table, vocab, width, out);
   });
   SB_CHECK_LAUNCH("sb_embed");
   return SB_OK;

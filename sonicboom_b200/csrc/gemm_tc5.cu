@@ -651,15 +651,6 @@ extern "C" size_t sb_gemm_tc5_scratch_bytes(int M, int N, int K, int n_sms) {
   return (size_t)tiles * splits * swapped_bn(M) * BM * sizeof(float);
 }
 
-// An RMSNorm of the product's rows, asked for together with the product.
-struct NormRequest {
-  const void* weight;
-  int weight_dtype;
-  float eps;
-  void* out;
-  int out_dtype;
-};
-
 extern "C" int sb_rmsnorm(const float* x, const int32_t* rows, int n_rows, int width,
                           const void* weight, int weight_dtype, float eps, void* out,
                           int out_dtype, cudaStream_t stream);
@@ -679,26 +670,27 @@ extern "C" int sb_gemm_tc5_fuses_norm(int M, int N, int K, int n_sms, int epilog
 static int tc5_run(const void* A, int a_dtype, const void* W, int w_dtype, int M, int N,
                    int K, int epilogue, const void* bias, int bias_dtype,
                    const float* residual, void* out, int out_dtype, void* scratch,
-                   size_t scratch_bytes, int n_sms, int form, const NormRequest* norm,
+                   size_t scratch_bytes, int n_sms, int form, const SbLinearExtras* extras,
                    cudaStream_t stream) {
+  const SbLinearExtras* norm = extras && extras->norm_weight ? extras : nullptr;
   if (int rc = sb_check_linear_args("sb_gemm_tc5", M, N, K, epilogue, bias, residual, out_dtype))
     return rc;
   if (norm) {
     if (epilogue == SB_EPI_SWIGLU || out_dtype != SB_F32)
       SB_FAIL(SB_ERR_UNSUPPORTED, "sb_gemm_tc5: a norm follows a float32 product without SwiGLU");
-    if (!norm->weight || !norm->out || !sb_valid_dtype(norm->weight_dtype) ||
-        !sb_valid_dtype(norm->out_dtype) || !(norm->eps >= 0.0f))
-      SB_FAIL(SB_ERR_ARG, "sb_gemm_tc5: norm weight, output, dtype codes %d %d or eps %g",
-              norm->weight_dtype, norm->out_dtype, norm->eps);
+    if (!norm->norm_out || !sb_valid_dtype(norm->norm_weight_dtype) ||
+        !sb_valid_dtype(norm->norm_out_dtype) || !(norm->norm_eps >= 0.0f))
+      SB_FAIL(SB_ERR_ARG, "sb_gemm_tc5: norm output, dtype codes %d %d or eps %g",
+              norm->norm_weight_dtype, norm->norm_out_dtype, norm->norm_eps);
     if (!norm_fuses(M, N, K, n_sms, epilogue, out_dtype, form) ||
-        (((uintptr_t)norm->weight | (uintptr_t)norm->out | (uintptr_t)out | (uintptr_t)residual |
-          (uintptr_t)bias) & 15)) {
+        (((uintptr_t)norm->norm_weight | (uintptr_t)norm->norm_out | (uintptr_t)out |
+          (uintptr_t)residual | (uintptr_t)bias) & 15)) {
       // the product as usual, then the norm as a kernel of its own
       if (int rc = tc5_run(A, a_dtype, W, w_dtype, M, N, K, epilogue, bias, bias_dtype, residual,
                            out, out_dtype, scratch, scratch_bytes, n_sms, form, nullptr, stream))
         return rc;
-      return sb_rmsnorm((const float*)out, nullptr, M, N, norm->weight, norm->weight_dtype,
-                        norm->eps, norm->out, norm->out_dtype, stream);
+      return sb_rmsnorm((const float*)out, nullptr, M, N, norm->norm_weight, norm->norm_weight_dtype,
+                        norm->norm_eps, norm->norm_out, norm->norm_out_dtype, stream);
     }
   }
   if (a_dtype != SB_BF16 || w_dtype != SB_BF16)
@@ -785,10 +777,10 @@ static int tc5_run(const void* A, int a_dtype, const void* W, int w_dtype, int M
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = (sb_pdl_enabled() & SB_K_REDUCE) ? 2 : 1;
-    SB_DISPATCH_DTYPE(norm->weight_dtype, TW, {
-      SB_DISPATCH_DTYPE(norm->out_dtype, TN, {
-        cudaLaunchKernelEx(&cfg, tc5_reduce_norm_kernel<TW, TN>, p, bn, (const TW*)norm->weight,
-                           norm->eps, (TN*)norm->out);
+    SB_DISPATCH_DTYPE(norm->norm_weight_dtype, TW, {
+      SB_DISPATCH_DTYPE(norm->norm_out_dtype, TN, {
+        cudaLaunchKernelEx(&cfg, tc5_reduce_norm_kernel<TW, TN>, p, bn, (const TW*)norm->norm_weight,
+                           norm->norm_eps, (TN*)norm->norm_out);
       });
     });
     SB_CHECK_LAUNCH("sb_gemm_tc5 (reduce + norm)");
@@ -811,15 +803,14 @@ extern "C" int sb_gemm_tc5(const void* A, int a_dtype, const void* W, int w_dtyp
                  out_dtype, scratch, scratch_bytes, n_sms, form, nullptr, stream);
 }
 
-// The product, and norm_out = RMSNorm(out) * norm_weight over the rows of the float32 result:
-// one kernel with the split-K sum where that form runs, else a norm kernel after the product.
-extern "C" int sb_gemm_tc5_norm(const void* A, int a_dtype, const void* W, int w_dtype, int M,
-                                int N, int K, int epilogue, const void* bias, int bias_dtype,
-                                const float* residual, void* out, int out_dtype, void* scratch,
-                                size_t scratch_bytes, int n_sms, int form, const void* norm_weight,
-                                int norm_weight_dtype, float norm_eps, void* norm_out,
-                                int norm_out_dtype, cudaStream_t stream) {
-  const NormRequest norm = {norm_weight, norm_weight_dtype, norm_eps, norm_out, norm_out_dtype};
+// The product with what may accompany it (see SbLinearExtras).  norm_out = RMSNorm(out) *
+// norm_weight over the rows of the float32 result comes from one kernel with the split-K sum
+// where that form runs, else from a norm kernel after the product.
+extern "C" int sb_gemm_tc5_ex(const void* A, int a_dtype, const void* W, int w_dtype, int M, int N,
+                              int K, int epilogue, const void* bias, int bias_dtype,
+                              const float* residual, void* out, int out_dtype, void* scratch,
+                              size_t scratch_bytes, int n_sms, int form,
+                              const SbLinearExtras* extras, cudaStream_t stream) {
   return tc5_run(A, a_dtype, W, w_dtype, M, N, K, epilogue, bias, bias_dtype, residual, out,
-                 out_dtype, scratch, scratch_bytes, n_sms, form, &norm, stream);
+                 out_dtype, scratch, scratch_bytes, n_sms, form, extras, stream);
 }

@@ -124,7 +124,7 @@ class DecodeLoop:
         self._replay()
         self.host_out.copy_(self.plan.tokens, non_blocking=True)
         torch.cuda.current_stream().synchronize()
-        return self.host_out.tolist()
+        return ops.check_tokens(self.host_out.tolist())
 
     def run_host(self, tokens, n_steps: int) -> list:
         for _ in range(n_steps):

@@ -74,11 +74,11 @@ def _i32(t, what):
 
 
 def embed(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """out[t] = table[tokens[t]] as float32."""
+    """out[t] = table[tokens[t]] as float32; an id outside the table gives a row of NaN."""
     n, width = tokens.numel(), table.shape[1]
     assert out.dtype == torch.float32 and out.shape == (n, width)
-    _check(lib().sb_embed(_i32(tokens, "tokens"), n, _ptr(table), _code(table.dtype), width,
-                          _ptr(out), _stream()), "embed")
+    _check(lib().sb_embed(_i32(tokens, "tokens"), n, _ptr(table), _code(table.dtype),
+                          table.shape[0], width, _ptr(out), _stream()), "embed")
     return out
 
 
@@ -147,22 +147,24 @@ def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = 
         fuses = fast and kernel in ("auto", "tc5") and bool(l.sb_gemm_tc5_fuses_norm(
             M, N, K, _sm_count(a.device), epilogue, _code(out.dtype), 0))
         if fuses and (kernel == "tc5" or FORCE_DECODE_KERNEL != "skinny"):
-            ws = _tc5_workspace(M, N, K, a.device)
-            _check(l.sb_gemm_tc5_norm(
-                *args[:-1], _ptr(ws), ctypes.c_size_t(ws.numel()), _sm_count(a.device), 0,
-                _ptr(norm_w), _code(norm_w.dtype), ctypes.c_float(norm_eps), _ptr(norm_out),
-                _code(norm_out.dtype), _stream()), "linear (tcgen05 kernel with norm)", launches=2)
+            kernel = "tc5"
+        else:
+            linear(a, w, out, epilogue, bias, residual, kernel)
+            rmsnorm(out, norm_w, norm_eps, norm_out)
             return out
-        linear(a, w, out, epilogue, bias, residual, kernel)
-        rmsnorm(out, norm_w, norm_eps, norm_out)
-        return out
     if kernel == "auto" and fast:
         kernel = _pick_kernel(M, N, K, a.device)
     if fast and kernel in ("tc5", "tc5_normal"):
         form = 1 if kernel == "tc5_normal" else 0
         ws = _tc5_workspace(M, N, K, a.device) if form == 0 else None
-        _check(l.sb_gemm_tc5(*args[:-1], _ptr(ws), ctypes.c_size_t(ws.numel() if ws is not None else 0),
-                             _sm_count(a.device), form, _stream()), "linear (tcgen05 kernel)",
+        extras = None
+        if norm is not None:
+            extras = LinearExtras(norm_w.data_ptr(), _code(norm_w.dtype), norm_eps,
+                                  norm_out.data_ptr(), _code(norm_out.dtype))
+        _check(l.sb_gemm_tc5_ex(*args[:-1], _ptr(ws), ctypes.c_size_t(ws.numel() if ws is not None else 0),
+                                _sm_count(a.device), form,
+                                ctypes.byref(extras) if extras is not None else None, _stream()),
+               "linear (tcgen05 kernel)",
                launches=2 if ws is not None else 1)        # a split product adds its reduce kernel
     elif fast and kernel == "skinny":
         _check(l.sb_gemm_skinny(*args), "linear (weight-streaming kernel)")
@@ -175,6 +177,22 @@ def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = 
     return out
 
 
+class LinearExtras(ctypes.Structure):
+    """SbLinearExtras of the kernel library: what may accompany a product."""
+    _fields_ = [("norm_weight", ctypes.c_void_p), ("norm_weight_dtype", ctypes.c_int),
+                ("norm_eps", ctypes.c_float), ("norm_out", ctypes.c_void_p),
+                ("norm_out_dtype", ctypes.c_int)]
+
+
+def _warm_args(warm):
+    """(pointer, bytes) of an L2 hint as the kernels take it."""
+    if warm is None or not WARM:
+        return _ptr(None), ctypes.c_size_t(0)
+    return _ptr(warm), ctypes.c_size_t(warm.numel() * warm.element_size())
+
+
+import os as _os
+WARM = _os.environ.get("SB_WARM", "1") != "0"       # L2 hints on (SB_WARM=0: off, for measurements)
 FORCE_DECODE_KERNEL = None      # "skinny" or "tc5": overrides the choice below (for measurements)
 
 
@@ -290,12 +308,14 @@ def attention_lib(head_dim: int):
 
 def attention(q: torch.Tensor, out: torch.Tensor, plan, group_index: int, cache: torch.Tensor,
               n_q_heads: int, n_kv_heads: int, head_dim: int, window: int, scale: float,
-              kernel: str = "auto") -> torch.Tensor:
+              kernel: str = "auto", warm: torch.Tensor | None = None) -> torch.Tensor:
     """Causal grouped-query attention of the step's rows over one cache entry's pages.
 
     bfloat16 runs the tensor-core kernels (built for the head size at first use); float32, a
     head size those kernels do not take, or `kernel="plain"` run the plain kernel.  `"mma"` keeps
-    prefill on the mma.sync kernel where the tensor-memory kernel would run (head sizes 64, 128)."""
+    prefill on the mma.sync kernel where the tensor-memory kernel would run (head sizes 64, 128).
+    `warm`: a tensor the kernel after this one will stream (weights); the decode kernel asks for
+    it into L2 while it merges its partial results.  A hint: it changes no result."""
     n = q.shape[0]
     g = plan.groups[group_index]
     al = attention_lib(head_dim) if (q.dtype == torch.bfloat16 and cache.dtype == torch.bfloat16
@@ -313,7 +333,7 @@ def attention(q: torch.Tensor, out: torch.Tensor, plan, group_index: int, cache:
             head_dim, window, ctypes.c_float(scale), _ptr(scratch),
             ctypes.c_size_t(scratch.numel() if scratch is not None else 0),
             _ptr(counters), counters.numel(), plan.max_len, cache.shape[0], _sm_count(q.device),
-            _stream())
+            *_warm_args(warm), _stream())
         if kernel == "mma":
             al.sb_attention_force_mma(0)
         if rc != 0:
@@ -344,7 +364,8 @@ def sample_params_size() -> int:
 def sample(logits: torch.Tensor, params: torch.Tensor, history: torch.Tensor | None,
            out_tokens: torch.Tensor, fed_pos: torch.Tensor | None = None) -> torch.Tensor:
     """One token per logits row; `params` is a uint8 tensor of packed per-row records.  With
-    `fed_pos` (int32 per row) the draw's position is fed_pos + 1 instead of the record's."""
+    `fed_pos` (int32 per row) the draw's position is fed_pos + 1 instead of the record's.
+    A row whose logits are not finite may get -1: `check_tokens` turns that into an error."""
     n, vocab = logits.shape
     assert logits.dtype == torch.float32 and params.dtype == torch.uint8
     assert params.numel() == n * sample_params_size()
@@ -354,6 +375,14 @@ def sample(logits: torch.Tensor, params: torch.Tensor, history: torch.Tensor | N
                            stride, _i32(fed_pos, "fed_pos") if fed_pos is not None else _ptr(None),
                            _i32(out_tokens, "out_tokens"), _stream()), "sample")
     return out_tokens
+
+
+def check_tokens(ids: list) -> list:
+    """Sampled ids as read on the host: raises where the sampler chose no token."""
+    bad = [i for i, t in enumerate(ids) if t < 0]
+    if bad:
+        raise KernelError(f"the sampler chose no token for row {bad[0]}: its logits are not finite")
+    return ids
 
 
 def add_i32(x: torch.Tensor, delta: int) -> torch.Tensor:

@@ -71,7 +71,7 @@ class Attention(Mixer):
                        g.page_size, storage if ctx.owns_cache else None, q)
         mixed = torch.empty((rows, self.qw), dtype=self.dtype, device=h.device)
         ops.attention(q, mixed, plan, ctx.kv_group(), storage, self.hq, self.hkv, self.hd,
-                      self.spec.window, self.spec.scale)
+                      self.spec.window, self.spec.scale, warm=self.w_o)
         out = residual if residual is not None else \
             torch.empty((rows, self.spec.width), dtype=torch.float32, device=h.device)
         return ctx.linear(mixed, self.w_o, out,

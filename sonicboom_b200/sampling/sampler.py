@@ -53,4 +53,4 @@ class Sampler:
         hist = torch.from_numpy(history).to(self.device) if history is not None else None
         out = torch.empty(logits.shape[0], dtype=torch.int32, device=self.device)
         ops.sample(logits, params, hist, out)
-        return out.cpu().tolist()
+        return ops.check_tokens(out.cpu().tolist())

@@ -41,6 +41,12 @@ def test_embed(dtype):
     out = torch.empty(5, 72, device=DEV)
     ops.embed(tokens, table, out)
     assert torch.equal(out, table.float()[tokens.long()])
+    # an id outside the table (what the sampler emits for logits that are not finite) reads
+    # nothing and gives a row of NaN
+    tokens = torch.tensor([-1, 2, 517, 2 ** 31 - 1], dtype=torch.int32, device=DEV)
+    out = torch.zeros(4, 72, device=DEV)
+    ops.embed(tokens, table, out)
+    assert torch.isnan(out[[0, 2, 3]]).all() and torch.equal(out[1], table.float()[2])
 
 
 @pytest.mark.parametrize("width", [8, 72, 1000, 3584])
@@ -470,6 +476,17 @@ def test_sampler_matches_the_plain_sampler():
                         for r in range(6)]
                 assert got == want, (vocab, s, position)
             assert torch.equal(logits, before)            # penalties were undone
+
+
+def test_logits_that_are_not_finite_are_an_error_not_a_token():
+    sampler = Sampler(DEV)
+    logits = torch.randn(3, 300).to(DEV)
+    logits[1, :] = float("nan")
+    with pytest.raises(ops.KernelError, match="row 1"):
+        sampler.sample(logits, [Sampling(temperature=0.7, seed=1).checked()] * 3, [0, 1, 2], [[], [], []])
+    logits[1, :] = 0.0
+    assert all(0 <= t < 300 for t in sampler.sample(
+        logits, [Sampling(temperature=0.7, seed=1).checked()] * 3, [0, 1, 2], [[], [], []]))
 
 
 def test_sampled_tokens_do_not_depend_on_the_row():
