@@ -98,13 +98,16 @@ static inline size_t sb_warm_bytes(const void* ptr, size_t bytes) {
   return (bytes < SB_WARM_MAX ? bytes : SB_WARM_MAX) & ~(size_t)15;
 }
 
-// What may accompany a product: the RMSNorm of its finished rows.
+// What may accompany a product (all optional): the RMSNorm of its finished rows, and memory to
+// ask into L2 for a later kernel.
 struct SbLinearExtras {
   const void* norm_weight;     // null: no norm
   int norm_weight_dtype;
   float norm_eps;
   void* norm_out;
   int norm_out_dtype;
+  const void* warm;            // null: nothing; else see sb_warm_l2
+  size_t warm_bytes;
 };
 
 // Kernel classes, as bits of the mask that says which kernels get the launch attribute.

@@ -55,6 +55,8 @@ struct Tc5Params {
   int tiles_a, tiles_b;        // tiles along the A rows and along the B rows
   int k_splits;                // swapped form: blocks that share one output tile
   float* scratch;              // swapped form with k_splits > 1: partial tiles [tile][split][BN][128]
+  const char* warm;            // asked into L2 by every block as it ends (or null)
+  size_t warm_bytes;
 };
 
 constexpr int stage_bytes(int bn) { return (BM + bn) * BK * 2; }
@@ -276,6 +278,10 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 
   tc_fence_before();
   __syncthreads();
+  // The block has read and written all it had to.  If the caller named weights that a later
+  // kernel streams but cannot request early itself (one launched without programmatic
+  // dependent launch), ask for them now: they arrive while the partial tiles are added.
+  if (p.warm_bytes && threadIdx.x == 0) sb_warm_l2(p.warm, p.warm_bytes, blockIdx.x, gridDim.x);
   if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
 
 }
@@ -705,6 +711,8 @@ static int tc5_run(const void* A, int a_dtype, const void* W, int w_dtype, int M
   Tc5Params p;
   p.M = M; p.N = N; p.K = K; p.epilogue = epilogue; p.bias = bias; p.bias_dtype = bias_dtype;
   p.residual = residual; p.out = out; p.k_splits = 1; p.scratch = nullptr;
+  p.warm = extras ? (const char*)extras->warm : nullptr;
+  p.warm_bytes = extras ? sb_warm_bytes(extras->warm, extras->warm_bytes) : 0;
   CUtensorMap ma, mb;
   // form: 0 picks by the number of rows, 1 forces the normal form, 2 the swapped form
   const bool normal = form == 1 || (form == 0 && M > 64);
@@ -805,7 +813,8 @@ extern "C" int sb_gemm_tc5(const void* A, int a_dtype, const void* W, int w_dtyp
 
 // The product with what may accompany it (see SbLinearExtras).  norm_out = RMSNorm(out) *
 // norm_weight over the rows of the float32 result comes from one kernel with the split-K sum
-// where that form runs, else from a norm kernel after the product.
+// where that form runs, else from a norm kernel after the product.  The L2 hint is taken by
+// the non-persistent kernel.
 extern "C" int sb_gemm_tc5_ex(const void* A, int a_dtype, const void* W, int w_dtype, int M, int N,
                               int K, int epilogue, const void* bias, int bias_dtype,
                               const float* residual, void* out, int out_dtype, void* scratch,

@@ -79,8 +79,10 @@ class DecoderModel:
             ctx.owns_cache = e.cache_from is None
             ctx.kv_entry = i if e.cache_from is None else e.cache_from
             # the next entry's first norm can ride on this entry's last product
-            ctx.after_block_norm = self.blocks[s.schedule[i + 1].layer].input_norm() \
-                if i + 1 < len(s.schedule) else None
+            nxt = self.blocks[s.schedule[i + 1].layer] if i + 1 < len(s.schedule) else None
+            ctx.after_block_norm = nxt.input_norm() if nxt is not None else None
+            # ... and its first weights can be asked into L2 meanwhile, if it would ask late
+            ctx.after_block_weights = nxt.first_weights(plan.n_rows) if nxt is not None else None
             x = self.blocks[e.layer].forward(x, ctx)
         if plan.n_want == 0:
             return None

@@ -108,12 +108,16 @@ def cast(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
 
 def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = EPI_NONE,
            bias: torch.Tensor | None = None, residual: torch.Tensor | None = None,
-           kernel: str = "auto", norm: tuple | None = None) -> torch.Tensor:
+           kernel: str = "auto", norm: tuple | None = None,
+           warm: torch.Tensor | None = None) -> torch.Tensor:
     """out = a @ w.T with a fused epilogue; a [M,K], w [N,K]; float32 accumulation.
 
     `norm` = (weight, eps, norm_out) also writes norm_out = rmsnorm(out, weight, eps) [M,N]
     (out must be float32): in the kernel that finishes the product where one does (the split-K
     decode form of the tcgen05 kernel), else with the norm kernel after it.
+    `warm`: weights that a later kernel streams; the blocks of the tcgen05 kernel ask for them
+    into L2 as they end (other kernels ignore it).  A hint: it changes no result.  It pays only
+    for a consumer that cannot request its own weights early (see `requests_weights_late`).
 
     bfloat16 operands run on tensor cores: `kernel` "tc5" (TMA + tcgen05), "skinny" (weights
     streamed into mma.sync fragments, at most SKINNY_MAX_ROWS rows), "tiled" (mma.sync tiles),
@@ -149,7 +153,7 @@ def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = 
         if fuses and (kernel == "tc5" or FORCE_DECODE_KERNEL != "skinny"):
             kernel = "tc5"
         else:
-            linear(a, w, out, epilogue, bias, residual, kernel)
+            linear(a, w, out, epilogue, bias, residual, kernel, warm=warm)
             rmsnorm(out, norm_w, norm_eps, norm_out)
             return out
     if kernel == "auto" and fast:
@@ -158,9 +162,14 @@ def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = 
         form = 1 if kernel == "tc5_normal" else 0
         ws = _tc5_workspace(M, N, K, a.device) if form == 0 else None
         extras = None
-        if norm is not None:
-            extras = LinearExtras(norm_w.data_ptr(), _code(norm_w.dtype), norm_eps,
-                                  norm_out.data_ptr(), _code(norm_out.dtype))
+        if norm is not None or (warm is not None and WARM):
+            extras = LinearExtras()
+            if norm is not None:
+                extras.norm_weight, extras.norm_weight_dtype = norm_w.data_ptr(), _code(norm_w.dtype)
+                extras.norm_eps, extras.norm_out = norm_eps, norm_out.data_ptr()
+                extras.norm_out_dtype = _code(norm_out.dtype)
+            if warm is not None and WARM:
+                extras.warm, extras.warm_bytes = warm.data_ptr(), warm.numel() * warm.element_size()
         _check(l.sb_gemm_tc5_ex(*args[:-1], _ptr(ws), ctypes.c_size_t(ws.numel() if ws is not None else 0),
                                 _sm_count(a.device), form,
                                 ctypes.byref(extras) if extras is not None else None, _stream()),
@@ -181,7 +190,8 @@ class LinearExtras(ctypes.Structure):
     """SbLinearExtras of the kernel library: what may accompany a product."""
     _fields_ = [("norm_weight", ctypes.c_void_p), ("norm_weight_dtype", ctypes.c_int),
                 ("norm_eps", ctypes.c_float), ("norm_out", ctypes.c_void_p),
-                ("norm_out_dtype", ctypes.c_int)]
+                ("norm_out_dtype", ctypes.c_int), ("warm", ctypes.c_void_p),
+                ("warm_bytes", ctypes.c_size_t)]
 
 
 def _warm_args(warm):
@@ -210,6 +220,15 @@ def _pick_kernel(M: int, N: int, K: int, device) -> str:
     if tiles >= _sm_count(device) or K >= 8192:
         return "tc5"
     return "skinny"
+
+
+def requests_weights_late(M: int, N: int, K: int, device) -> bool:
+    """Whether the bfloat16 product kernel that "auto" picks for these sizes starts only when
+    the kernel before it has ended (it is launched without programmatic dependent launch), so
+    that its weights are worth an L2 hint from an earlier kernel."""
+    kernel = _pick_kernel(M, N, K, device)
+    cls = {"tc5": PDL_TC5, "skinny": PDL_SKINNY}[kernel]
+    return not (int(lib().sb_pdl_enabled()) & cls)
 
 
 _sm_counts: dict = {}

@@ -55,6 +55,11 @@ class Attention(Mixer):
             self.b_qkv = _cat([get(p + f"{n}_proj.bias") for n in "qkv"])
         self.w_o = get(p + "o_proj.weight")
 
+    def first_weights(self, rows):
+        n, k = self.w_qkv.shape
+        late = self.w_qkv.dtype == torch.bfloat16 and ops.requests_weights_late(rows, n, k, self.w_qkv.device)
+        return self.w_qkv if late else None
+
     def forward(self, h, ctx, residual=None):
         rows = h.shape[0]
         plan = ctx.plan

@@ -20,6 +20,11 @@ the normed rows back through `ctx.take_normed(norm, rows)`.  Across blocks the m
 next entry's first norm in `ctx.after_block_norm`, and a block whose result is its last part's
 result passes it on as that part's `next_norm`.  Parts and blocks that ignore all this are still
 right: `take_normed` then returns None and the caller runs the norm itself.
+
+`ctx.next_weights` is a hint of the same kind: weights that something after the running part
+streams and cannot request early itself (`first_weights(rows)` of a part or block says which).
+`ctx.linear` passes it to the product kernel, whose blocks ask for it into L2 as they end.  A
+hint changes no result, and ignoring it costs nothing.
 """
 from __future__ import annotations
 
@@ -42,6 +47,8 @@ class StepContext:
     owns_cache: bool = True
     next_norm: Optional["Norm"] = None     # the norm the caller applies to the running part's result
     after_block_norm: Optional["Norm"] = None   # the first norm of the entry that runs next (for blocks)
+    next_weights: Optional[torch.Tensor] = None         # an L2 hint for the running part's last product
+    after_block_weights: Optional[torch.Tensor] = None  # what the entry that runs next streams first, if it asks late
     _normed: Optional[tuple] = None        # (norm, rows, normed rows) of the last `linear` that had one
 
     def linear(self, a, w, out, epilogue, residual=None, bias=None, act_dtype=None):
@@ -49,11 +56,13 @@ class StepContext:
         its result over the finished rows (in `act_dtype`) is produced with it and kept for
         `take_normed`."""
         norm, self.next_norm, self._normed = self.next_norm, None, None
+        warm, self.next_weights = self.next_weights, None
         rms = norm.as_rms() if norm is not None else None
         if rms is None or out.dtype != torch.float32 or epilogue == ops.EPI_SWIGLU:
-            return ops.linear(a, w, out, epilogue, bias=bias, residual=residual)
+            return ops.linear(a, w, out, epilogue, bias=bias, residual=residual, warm=warm)
         normed = torch.empty(out.shape, dtype=act_dtype or a.dtype, device=out.device)
-        ops.linear(a, w, out, epilogue, bias=bias, residual=residual, norm=(rms[0], rms[1], normed))
+        ops.linear(a, w, out, epilogue, bias=bias, residual=residual, norm=(rms[0], rms[1], normed),
+                   warm=warm)
         self._normed = (norm, out, normed)
         return out
 
@@ -116,6 +125,11 @@ class Mixer(Part):
     def forward(self, h, ctx: StepContext, residual=None):
         raise NotImplementedError
 
+    def first_weights(self, rows: int) -> Optional[torch.Tensor]:
+        """The weights its forward streams first, if at `rows` rows they are worth an L2 hint
+        from whatever runs before it (`ops.requests_weights_late`); else None."""
+        return None
+
 
 class FeedForward(Part):
     """forward(h [rows, width], ctx, residual=None) -> float32 [rows, width]."""
@@ -133,6 +147,10 @@ class Block(Part):
     def input_norm(self) -> Optional[Norm]:
         """The norm this arrangement applies to its input first, if it starts with one: the
         entry before it may then deliver the normed rows (see `StepContext.take_normed`)."""
+        return None
+
+    def first_weights(self, rows: int) -> Optional[torch.Tensor]:
+        """As `Mixer.first_weights`, for the block's first product."""
         return None
 
     def kv_need(self):

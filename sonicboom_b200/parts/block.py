@@ -32,6 +32,9 @@ class PreNormBlock(Block):
     def input_norm(self):
         return self.mixer_norm
 
+    def first_weights(self, rows):
+        return self.mixer.first_weights(rows)
+
     def forward(self, x, ctx):
         h = ctx.take_normed(self.mixer_norm, x)
         if h is None:
@@ -41,5 +44,6 @@ class PreNormBlock(Block):
         f = ctx.take_normed(self.feed_forward_norm, x)
         if f is None:
             f = self.feed_forward_norm.forward(x, self.dtype)
-        ctx.next_norm = ctx.after_block_norm       # the block's result is the feed-forward's
+        # the block's result is the feed-forward's, so what follows the block follows its product
+        ctx.next_norm, ctx.next_weights = ctx.after_block_norm, ctx.after_block_weights
         return self.feed_forward.forward(f, ctx, residual=x)
