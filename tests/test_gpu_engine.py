@@ -91,6 +91,38 @@ def test_a_long_context(tmp_path, dtype):
     assert ops.tc5_status() == 0 and ops.attention_status(TINY["B"]["head_dim"]) == 0
 
 
+def test_a_norm_computed_with_the_product_before_it_changes_nothing(tmp_path, monkeypatch):
+    """A wider configuration (8 heads of 64, intermediate 1,024), so that the kernel that adds
+    the split o and down products also norms their rows in decoding.  With that hand-over
+    switched off (every norm a kernel of its own) the logits agree to float32 rounding: the
+    operands of every product differ by at most an ulp of bfloat16 in a few elements."""
+    import sonicboom_b200 as sb
+    from sonicboom_b200 import ops
+    from sonicboom_b200.parts.base import StepContext
+    cfg = dict(TINY["B"], hidden_size=256, num_attention_heads=8, num_key_value_heads=2,
+               intermediate_size=1024)
+    sb.write_random_model(tmp_path, cfg, seed=5, std=0.05)
+    eng = engine_for({"W": tmp_path}, "W", "bfloat16")
+    reqs = prompts_for("B", [40, 9], seed=8)
+    used = []
+    real = ops.lib().sb_gemm_tc5_fuses_norm
+
+    def spy(*a):
+        used.append(bool(real(*a)))
+        return real(*a)
+    monkeypatch.setattr(ops.lib(), "sb_gemm_tc5_fuses_norm", spy, raising=False)
+    handed = batch_unequal(eng, reqs, [len(r) - 6 for r in reqs])
+    assert any(used)
+    monkeypatch.setattr(StepContext, "take_normed", lambda self, norm, x: None)
+    plain = batch_unequal(eng, reqs, [len(r) - 6 for r in reqs])
+    for h, p_ in zip(handed, plain):
+        assert pm.rel_err(h, p_) < 2e-3
+    pcfg, tensors = pm.read_model_dir(tmp_path)
+    for r, h in zip(reqs, handed):
+        assert pm.rel_err(h, pm.forward(pcfg, tensors, r)) < BF16_TOL
+    assert ops.tc5_status() == 0
+
+
 @pytest.mark.parametrize("name,dtype", CASES)
 def test_first_tokens_of_a_sequence(model_dirs, oracles, name, dtype):
     eng = engine_for(model_dirs, name, dtype)
