@@ -17,7 +17,7 @@ uses for one Qwen2 block (core/src/model/emit.cpp:255-308, 364-374, 436-459, 512
 Unlike the reference's graph, the driver does not round K and V through float16 (the reference's
 CastFp16 nodes, emit.cpp:291-293): the golden values pin the formulas, not that storage choice.
 
-    python tests/golden/make_golden.py [/root/reference]
+    python tests/golden/make_golden.py <checkout of hardenedlinux/SonicBoom>
 
 Needs g++ with C++23.  The JSON it writes is committed; the test does not need the reference.
 """
@@ -30,7 +30,9 @@ from pathlib import Path
 import numpy as np
 
 HERE = Path(__file__).resolve().parent
-REF = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+if len(sys.argv) != 2:
+    sys.exit(__doc__)
+REF = Path(sys.argv[1])
 
 # a tiny one-layer model: 3 query heads over 1 key/value head of 8, width 24, intermediate 40
 CFG = dict(d=24, hq=3, hkv=1, hd=8, ff=40, vocab=50, n=7, eps=1e-5, theta=10000.0, window=3)
