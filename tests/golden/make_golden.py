@@ -30,9 +30,6 @@ from pathlib import Path
 import numpy as np
 
 HERE = Path(__file__).resolve().parent
-if len(sys.argv) != 2:
-    sys.exit(__doc__)
-REF = Path(sys.argv[1])
 
 # a tiny one-layer model: 3 query heads over 1 key/value head of 8, width 24, intermediate 40
 CFG = dict(d=24, hq=3, hkv=1, hd=8, ff=40, vocab=50, n=7, eps=1e-5, theta=10000.0, window=3)
@@ -155,6 +152,9 @@ def make_inputs():
 
 
 def main() -> int:
+    if len(sys.argv) != 2:
+        sys.exit(__doc__)
+    REF = Path(sys.argv[1])
     c = CFG
     tensors = make_inputs()
     with tempfile.TemporaryDirectory() as tmp:
