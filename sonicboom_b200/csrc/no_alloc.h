@@ -16,7 +16,8 @@
 // Limits and rules:
 //  * Decode steps only: new rows per sequence x (query heads / key-value heads) <= 16.
 //  * The step must need at most SB_STATIC_SCRATCH_BYTES of scratch, i.e.
-//    rows x query heads x ceil(max_len / 256) x (head size + 2) x 4 bytes; larger steps are
+//    rows x query heads x splits x (head size + 4) x 4 bytes, with splits = ceil(max_len / 256)
+//    up to 4,096 keys and max(16, ceil(max_len / 512)) beyond; larger steps are
 //    refused with SB_ERR_UNSUPPORTED and a message that states both numbers.
 //  * The first call on a device looks the array's device address up (cudaGetSymbolAddress,
 //    with that device current) and remembers it; make that first call outside any stream
