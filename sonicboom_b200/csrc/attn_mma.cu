@@ -473,17 +473,19 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(const AttnP
 
   // The block that finishes last for this (sequence, key/value head) merges its splits in
   // ascending order; the counter is left at zero for the next launch.
-  __threadfence();
+  // Release / acquire through the counter: the block's partial results are ordered before
+  // thread 0's atomic by the barrier, the atomic releases them device-wide, and the last
+  // block's atomic acquires every earlier block's; the barrier after it orders the reads below.
   __syncthreads();
   if (tid == 0) {
     int* counter = p.counters + (size_t)b * p.n_kv_heads + kvh;
-    const int seen = atomicAdd(counter, 1);
+    int seen;
+    asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;\n" : "=r"(seen) : "l"(counter) : "memory");
     s_last = seen == split_hi - split_lo;
     if (s_last) *counter = 0;
   }
   __syncthreads();
   if (!s_last) return;
-  __threadfence();
   // Final merge.  The splits' (m, l) go to shared memory first, one thread per row turns
   // them into weights exp2(m_s - max) and the row's 1 / sum, and then four values of a row
   // are a weighted sum over the splits whose loads are independent of each other and issued
