@@ -183,3 +183,12 @@ def test_packed_sampler_records():
     assert abs(float(r["temperature"][0]) - 0.7) < 1e-6
     rec, hist = pack_params([b], [0], [[1, 2]])
     assert hist is None
+
+
+def test_a_row_without_a_sampled_token_is_an_error():
+    """The device sampler writes -1 where no candidate survives (logits that are not finite);
+    wherever ids are read on the host that becomes an error that names the row."""
+    from sonicboom_b200 import ops
+    assert ops.check_tokens([3, 0, 7]) == [3, 0, 7]
+    with pytest.raises(ops.KernelError, match="row 1"):
+        ops.check_tokens([3, -1, 7])
