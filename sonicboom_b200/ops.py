@@ -208,11 +208,13 @@ FORCE_DECODE_KERNEL = None      # "skinny" or "tc5": overrides the choice below 
 
 def _pick_kernel(M: int, N: int, K: int, device) -> str:
     """Which bfloat16 product kernel "auto" means.  The tcgen05 kernel, except for small
-    matrices at up to 16 rows: there the kernel that streams W into mma.sync fragments has lower
-    fixed costs (measured on B200 at the 7B layer sizes, inside CUDA graphs: 9 us against 12 us
-    for the 4608 x 3584 and 3584 x 3584 products at 8 rows, equal at 16 rows, while at 64 rows
-    the tcgen05 kernel takes 12 us and the streaming kernel 19 us)."""
-    if M > 16:
+    matrices at up to 8 rows: there the kernel that streams W into mma.sync fragments has lower
+    fixed costs (measured on B200 at the 7B layer sizes, alone inside CUDA graphs: 9 us against
+    12 us for the 4608 x 3584 product at 8 rows, while at 64 rows the tcgen05 kernel takes 12 us
+    and the streaming kernel 19 us; inside the decode step, where the tcgen05 kernel requests its
+    weights while the kernel before it ends, the streaming kernel wins by 0.5 % of the step at
+    8 rows and loses by 1.3 % at 16)."""
+    if M > 8:
         return "tc5"
     if FORCE_DECODE_KERNEL:
         return FORCE_DECODE_KERNEL
