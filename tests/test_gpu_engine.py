@@ -160,3 +160,41 @@ def test_refusals_reach_the_caller(model_dirs):
     with pytest.raises(CacheFull):
         eng.step([(t, [1] * 10, [])])
     assert eng.step([(s, [2], [])]) is None
+
+
+def test_layers_of_a_7b_model_decode_as_they_prefill():
+    """Two layers with the sizes of a 7B model (width 3,584, 28/4 heads of 128, intermediate
+    18,944) and requests of 8,224 and 3,032 tokens: whole in one step, and with the last 32
+    tokens one by one in a batch of two.  The prompt runs the persistent tcgen05 products and
+    the tensor-memory attention over 129 pages; decoding runs the split products with the norm
+    in their reduce kernel, and key splits of 512 (the long request) and 256 (the short one).
+    No oracle at this size: the two cuts are held against each other."""
+    import sonicboom_b200 as sb
+    from sonicboom_b200 import ops
+    cfg = dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", hidden_size=3584,
+               num_hidden_layers=2, num_attention_heads=28, num_key_value_heads=4,
+               intermediate_size=18944, vocab_size=32000, rope_theta=1000000.0, rms_norm_eps=1e-6,
+               max_position_embeddings=16384, tie_word_embeddings=False)
+    model = sb.random_model(cfg, seed=3, dtype="bfloat16", device="cuda:0", std=0.02)
+    eng = sb.Engine(model, max_tokens=16384)
+    g = torch.Generator().manual_seed(11)
+    reqs = [torch.randint(0, 32000, (n,), generator=g).tolist() for n in (8224, 3032)]
+    tail = 32
+    slots = [eng.open() for _ in reqs]
+    whole = eng.step([(s, r, list(range(len(r) - tail, len(r)))) for s, r in zip(slots, reqs)]).float().cpu()
+    for s in slots:
+        eng.close(s)
+    slots = [eng.open() for _ in reqs]
+    assert eng.step([(s, r[:-tail], []) for s, r in zip(slots, reqs)]) is None
+    steps = [eng.step([(s, [r[len(r) - tail + t]], [0]) for s, r in zip(slots, reqs)]).float().cpu()
+             for t in range(tail)]
+    for s in slots:
+        eng.close(s)
+    for i in range(len(reqs)):
+        cut = torch.stack([st[i] for st in steps])
+        ref = whole[i * tail:(i + 1) * tail]
+        per_pos = (cut - ref).abs().amax(dim=1) / ref.abs().max()
+        assert float(per_pos.max()) < BF16_TOL, f"request {i}: worst position {int(per_pos.argmax())}"
+    assert ops.tc5_status() == 0 and ops.attention_status(128) == 0
+    del eng, model
+    torch.cuda.empty_cache()
