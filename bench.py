@@ -39,9 +39,18 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"
 def peaks() -> dict:
     p = ROOT / "MEASURED_PEAKS.json"
     if p.is_file():
+        def find(d, key):
+            """The number under `key`, at the top or one dictionary down."""
+            if isinstance(d, dict):
+                if isinstance(d.get(key), (int, float)):
+                    return float(d[key])
+                for v in d.values():
+                    if isinstance(v, dict) and isinstance(v.get(key), (int, float)):
+                        return float(v[key])
+            raise KeyError(key)
         try:
             d = json.loads(p.read_text())
-            return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+            return {"hbm_gbs": find(d, "hbm_gbs"), "bf16_tflops": find(d, "bf16_tflops"),
                     "source": "measured"}
         except (ValueError, KeyError, TypeError):
             pass
