@@ -13,7 +13,10 @@
 //   swapped  A = weights (128 weight rows per tile), B = activations (up to 64 rows): the
 //            decode product, which is bound by reading the weights once.  K may be split over
 //            several blocks; their partial tiles go to scratch memory and a second kernel adds
-//            them in split order and runs the epilogue, so the sum's order is fixed.
+//            them in split order and runs the epilogue, so the sum's order is fixed.  That
+//            second kernel can also apply the RMSNorm that follows the product
+//            (tc5_reduce_norm_kernel: a cluster of blocks per row, the sum of squares over
+//            distributed shared memory).
 //
 // Every wait on an mbarrier is bounded; when a bound is hit the kernel records a code in a
 // status word, stops issuing work and leaves normally (sb_tc5_status reads the word).
