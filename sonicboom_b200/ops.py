@@ -229,7 +229,7 @@ def requests_weights_late(M: int, N: int, K: int, device) -> bool:
     the kernel before it has ended (it is launched without programmatic dependent launch), so
     that its weights are worth an L2 hint from an earlier kernel."""
     kernel = _pick_kernel(M, N, K, device)
-    cls = {"tc5": PDL_TC5, "skinny": PDL_SKINNY}[kernel]
+    cls = PDL_TC5 if kernel == "tc5" else PDL_SKINNY
     return not (int(lib().sb_pdl_enabled()) & cls)
 
 
