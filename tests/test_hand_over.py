@@ -92,3 +92,70 @@ def test_an_l2_hint_goes_with_the_next_product_only(monkeypatch):
     ctx.linear(a, w, out, ops.EPI_NONE)
     ctx.linear(a, w, out, ops.EPI_NONE)
     assert calls[0]["warm"] is hint and calls[1]["warm"] is None
+
+
+# ------------------------------------------------------------------ the block's use of it
+def build_block(monkeypatch, mixer_hands_over: bool):
+    """A pre-norm block out of toy parts registered for this test: norms that count their own
+    runs, a mixer and a feed-forward that add 1 to the residual; the mixer leaves the next norm's
+    result behind (as a product kernel would) only if asked to."""
+    from sonicboom_b200 import parts
+    from sonicboom_b200.config.specs import FeedForwardSpec, LayerSpec, MixerSpec, NormSpec
+    from sonicboom_b200.parts.base import BLOCKS, FeedForward, Mixer
+
+    runs = []
+
+    class CountingNorm(RmsLike):
+        def __init__(self, spec, dtype, device):
+            super().__init__(spec.width)
+            self.name = spec.tensor
+
+        def forward(self, x, out_dtype, rows=None):
+            runs.append(self.name)
+            return x.to(out_dtype)
+
+    class AddOne(Mixer):
+        def __init__(self, spec, dtype, device):
+            pass
+
+        def forward(self, h, ctx, residual=None):
+            out = residual.add_(1.0)
+            if mixer_hands_over and ctx.next_norm is not None:
+                ctx._normed = (ctx.next_norm, out, out.to(torch.bfloat16))
+            return out
+
+    class AddOneFF(FeedForward):
+        def __init__(self, spec, dtype, device):
+            pass
+
+        def forward(self, h, ctx, residual=None):
+            assert ctx.next_norm is ctx.after_block_norm       # what follows the block follows it
+            return residual.add_(1.0)
+
+    monkeypatch.setitem(parts.base.NORMS, "counting", CountingNorm)
+    monkeypatch.setitem(parts.base.MIXERS, "add_one", AddOne)
+    monkeypatch.setitem(parts.base.FEED_FORWARDS, "add_one", AddOneFF)
+    spec = LayerSpec(arrangement="pre_norm", mixer=MixerSpec(kind="add_one", width=4),
+                     mixer_norm=NormSpec("counting", 4, 1e-5, "first"),
+                     feed_forward=FeedForwardSpec(kind="add_one", width=4, intermediate=8),
+                     feed_forward_norm=NormSpec("counting", 4, 1e-5, "second"))
+    return BLOCKS["pre_norm"](spec, torch.bfloat16, "cpu"), runs
+
+
+def test_a_block_runs_the_norms_itself_when_nothing_is_handed_over(monkeypatch):
+    block, runs = build_block(monkeypatch, mixer_hands_over=False)
+    ctx = StepContext(plan=None, cache=None)
+    x = torch.zeros(2, 4)
+    assert float(block.forward(x, ctx)[0, 0]) == 2.0
+    assert runs == ["first", "second"]
+    assert block.input_norm() is block.mixer_norm
+
+
+def test_a_block_takes_what_is_handed_over(monkeypatch):
+    block, runs = build_block(monkeypatch, mixer_hands_over=True)
+    ctx = StepContext(plan=None, cache=None)
+    x = torch.zeros(2, 4)
+    ctx._normed = (block.mixer_norm, x, x.to(torch.bfloat16))   # left by the entry before it
+    ctx.after_block_norm = RmsLike(4)
+    block.forward(x, ctx)
+    assert runs == []                                           # neither norm ran as its own kernel
