@@ -306,6 +306,7 @@ __global__ void __launch_bounds__(PREFILL_THREADS) attn_prefill_kernel(const Att
 // each other; three or four stages (two blocks or one per SM) measured 20.6 and 22.8 us
 // against 14.9 us per layer at batch 8, 3,072 keys, whatever the split length.
 constexpr int DEC_STAGES = 2;
+constexpr size_t WARM_MAX_CHUNKS = 48;   // most 16 KB prefetches a block issues for the L2 hint
 constexpr int DECODE_SMEM = (DEC_ROWS + 2 * DEC_STAGES * KT) * LDS * 2;
 constexpr int PART_STRIDE = HD + 4;    // floats per partial row: o[HD], m, l (rows stay 16-byte aligned)
 constexpr bool DECODE_FITS = DECODE_SMEM <= 227 * 1024;
@@ -648,6 +649,11 @@ extern "C" int sb_attention(const void* q, void* out, int n_rows, int n_seqs, in
     if (need && (!counters || n_counters < n_seqs * n_kv_heads))
       SB_FAIL(SB_ERR_ARG, "sb_attention: %d zeroed counters needed, %d given", n_seqs * n_kv_heads,
               n_counters);
+    // The L2 hint pays only when many SMs share it: a block's share goes through its SM's copy
+    // engine, and a few blocks with megabytes each hold the kernel up (a step of one 768-key
+    // sequence, 16 blocks: 2.5 us a layer slower than without the hint).
+    if ((size_t)p.n_splits * n_kv_heads * n_seqs * WARM_MAX_CHUNKS * SB_WARM_CHUNK < p.warm_bytes)
+      p.warm_bytes = 0;
     sb_launch<SB_K_ATTENTION>(attn_decode_kernel, dim3(p.n_splits, n_kv_heads, n_seqs), dim3(DEC_WARPS * 32),
               DECODE_SMEM, stream, p);
     SB_CHECK_LAUNCH("sb_attention (decode)");
