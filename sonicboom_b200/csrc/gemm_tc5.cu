@@ -764,6 +764,9 @@ static int tc5_run(const void* A, int a_dtype, const void* W, int w_dtype, int M
   if (!make_map(&ma, W, N, K, BM) || !make_map(&mb, A, M, K, bn))
     SB_FAIL(SB_ERR_CUDA, "sb_gemm_tc5: cuTensorMapEncodeTiled failed");
   const int blocks = p.tiles_a * splits;
+  // an L2 hint pays only when many blocks share it (each block's share goes through its SM's
+  // copy engine): at most 48 prefetches of 16 KB a block
+  if ((size_t)blocks * 48 * SB_WARM_CHUNK < p.warm_bytes) p.warm_bytes = 0;
   int rc;
   // stages are chosen so that two blocks fit an SM (about 100 KB of shared memory each)
 #define SB_TC5_SWAPPED(BN_, ST_)                                                             \
