@@ -187,7 +187,7 @@ def run(args) -> int:
         for s in slots:
             engine.cache.reserve(s, PROMPT_LEN + skip)
             engine.cache.advance(s, PROMPT_LEN + skip)
-        loop = DecodeLoop(engine, slots, max_new=warmup + steps + 2, use_graph=graph)
+        loop = DecodeLoop(engine, slots, warmup + steps + 2, use_graph=graph)
         loop.run_device(first, warmup)
         torch.cuda.synchronize()
         ctx_start = engine.length(slots[0]) + warmup

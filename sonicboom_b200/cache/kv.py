@@ -135,6 +135,25 @@ class Cache:
             if add > 0:
                 pages.extend(g.pool.take(add))
 
+    def reserve_many(self, wants) -> None:
+        """`reserve` for several sequences at once, `wants` being (slot, new_len) pairs: either
+        every one of them gets its pages or nothing changes (raises CacheFull)."""
+        wants = list(wants)
+        need = [0] * len(self.groups)
+        for slot, new_len in wants:
+            rec = self._record(slot)
+            if new_len < rec.length:
+                raise CacheError(f"slot {slot}: cannot shrink from {rec.length} to {new_len}")
+            want = (new_len + self.page_size - 1) // self.page_size
+            for gi, pages in enumerate(rec.pages):
+                need[gi] += max(0, want - len(pages))
+        for g, n in zip(self.groups, need):
+            if n > g.pool.free_count:
+                raise CacheFull(f"{len(wants)} sequences need {n} more page(s) of {self.page_size} "
+                                f"tokens together, {g.pool.free_count} of {g.pool.n} are free")
+        for slot, new_len in wants:
+            self.reserve(slot, new_len)
+
     def advance(self, slot: int, new_len: int) -> None:
         """Records the new length after a step and gives back pages a window has left behind."""
         rec = self._record(slot)
@@ -156,10 +175,13 @@ class Cache:
     def truncate(self, slot: int, new_len: int) -> bool:
         """Cuts a sequence back to its first `new_len` tokens (prefix reuse).  Returns False,
         changing nothing, when a windowed group has already given back pages that the shorter
-        sequence would read again."""
+        sequence would read again, or when the model keeps fixed-size state per sequence (it
+        was advanced by the tokens that would be cut)."""
         rec = self._record(slot)
         if not 0 <= new_len <= rec.length:
             raise CacheError(f"slot {slot}: cannot truncate from {rec.length} to {new_len}")
+        if self.state and new_len < rec.length:
+            return False         # fixed-size state has moved on with the tokens and cannot go back
         keep = (new_len + self.page_size - 1) // self.page_size
         for g, pages in zip(self.groups, rec.pages):
             first_seen = max(0, new_len - g.need.window + 1) // self.page_size if g.need.window else 0

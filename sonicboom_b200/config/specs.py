@@ -95,10 +95,16 @@ class ModelSpec:
     final_norm: NormSpec = None
     head_tensor: Optional[str] = None   # None: the head is the embedding matrix (tied)
     stop_tokens: tuple = ()
+    embedding_scale: float = 1.0        # multiplies every embedding row (1: as stored)
+    logit_cap: float = 0.0              # c > 0: logits = c * tanh(logits / c); 0: no cap
 
     def validate(self) -> None:
         if not self.layers:
             raise ConfigError("model has no layers")
+        if not self.embedding_scale > 0.0:
+            raise ConfigError(f"embedding_scale {self.embedding_scale} must be positive")
+        if self.logit_cap < 0.0:
+            raise ConfigError(f"logit_cap {self.logit_cap} must be zero (none) or positive")
         for i, e in enumerate(self.schedule):
             if not 0 <= e.layer < len(self.layers):
                 raise ConfigError(f"schedule[{i}] names layer {e.layer}, model has {len(self.layers)}")

@@ -235,6 +235,8 @@ __global__ void __launch_bounds__(PREFILL_THREADS) attn_prefill_kernel(const Att
   const int R = n_new * G;
   const int r_base = (int)(gridDim.x / p.n_kv_heads - 1 - blockIdx.x / p.n_kv_heads) * BM;
   if (r_base >= R) return;
+  // positions without pages in the sequence's own list: nothing is read
+  if (pos0 < 0 || (pos0 + n_new - 1) / KT >= p.page_off[b + 1] - p.page_off[b]) return;
   const int32_t* pages = p.page_ids + p.page_off[b];
 
   for (int idx = tid; idx < BM * (HD / 8); idx += PREFILL_THREADS) {
@@ -332,6 +334,20 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(const AttnP
   const int key_lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
   const int sp = split_pages_for(p_hi + 1);
   const int split_lo = key_lo / (sp * KT), split_hi = p_hi / (sp * KT);
+  // A sequence whose new positions have no pages in its own list (or more splits than the grid
+  // was sized for) attends to nothing: its rows are zeros, no other sequence's pages are read,
+  // and its merge counter is not touched.
+  const int n_own_pages = p.page_off[b + 1] - p.page_off[b];
+  if (pos0 < 0 || p_hi / KT >= n_own_pages || split_hi >= p.n_splits) {
+    sb_pdl_wait();
+    if (split == 0)
+      for (int item = tid; item < R * (HD / 4); item += DEC_WARPS * 32) {
+        const int row = item / (HD / 4), c = item % (HD / 4);
+        const size_t out_row = (size_t)(row0 + row / G) * p.n_q_heads + kvh * G + row % G;
+        *reinterpret_cast<uint2*>(p.out + out_row * HD + 4 * c) = make_uint2(0u, 0u);
+      }
+    return;
+  }
   if (split < split_lo || split > split_hi) return;
   const int32_t* pages = p.page_ids + p.page_off[b];
   const int tile_lo = max(split * sp, key_lo / KT);
@@ -340,7 +356,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(const AttnP
   int page_of[LONG_SPLIT_PAGES];
 #pragma unroll
   for (int i = 0; i < LONG_SPLIT_PAGES; ++i)
-    page_of[i] = tile_lo + i <= tile_hi ? pages[tile_lo + i] : 0;
+    page_of[i] = tile_lo + i <= tile_hi ? max(pages[tile_lo + i], 0) : 0;   // never an address before the cache
   const bool first_is_old = (tile_lo + 1) * KT <= pos0;
   if (first_is_old)
     load_kv_tile(kv0, kv0 + KT * LDS * 2, p.cache, page_of[0], p.n_kv_heads, kvh, tid, DEC_WARPS * 32);

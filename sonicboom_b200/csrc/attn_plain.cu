@@ -34,8 +34,15 @@ attn_plain_kernel(const TQ* q, TQ* out, const int32_t* row_seq, const int32_t* r
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int kvh = h / (n_q_heads / n_kv_heads);
   const int pos = row_pos[t];
-  const int32_t* pages = page_ids + page_off[row_seq[t]];
+  const int seq = row_seq[t];
+  const int32_t* pages = page_ids + page_off[seq];
   const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  // a position without a page in the sequence's own list: the row is zeros, nothing is read
+  if (pos < 0 || pos / page_size >= page_off[seq + 1] - page_off[seq]) {
+    for (int d = tid; d < hd; d += THREADS)
+      out[((size_t)t * n_q_heads + h) * hd + d] = sb_from_f32<TQ>(0.0f);
+    return;
+  }
 
   for (int d = tid; d < hd; d += THREADS)
     qs[d] = sb_to_f32<TQ>(q[((size_t)t * n_q_heads + h) * hd + d]);

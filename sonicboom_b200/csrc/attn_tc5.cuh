@@ -132,6 +132,8 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_kv, const AttnPa
   const int R = n_new * G;
   const int r_base = (int)(gridDim.x / p.n_kv_heads - 1 - blockIdx.x / p.n_kv_heads) * (T5_QT * T5_ROWS);
   if (r_base >= R) return;
+  // positions without pages in the sequence's own list: nothing is read
+  if (pos0 < 0 || (pos0 + n_new - 1) / KT >= p.page_off[b + 1] - p.page_off[b]) return;
   const int r_last = min(R, r_base + T5_QT * T5_ROWS) - 1;
   const int tile_lo = (p.window > 0 ? max(0, pos0 + r_base / G - p.window + 1) : 0) / KT;
   const int tile_hi = (pos0 + r_last / G) / KT;

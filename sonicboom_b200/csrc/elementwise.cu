@@ -5,8 +5,9 @@
 extern "C" int sb_abi_version() { return 1; }
 
 // ------------------------------------------------------------------------------- embedding
-// x[t, :] = E[tokens[t], :] as float32; no sqrt(width) scale for this architecture
-// (core/src/model/emit.cpp:237-247, core/src/nn/embedding.cpp:23-28).
+// x[t, :] = E[tokens[t], :] * scale as float32.  The scale is the model's (1 for this
+// architecture; the reference multiplies by sqrt(width) for the architectures whose trait says
+// so: core/src/model/emit.cpp:237-247, core/src/nn/embedding.cpp:23-28); 1 multiplies nothing.
 // Inputs that an earlier kernel of the step wrote are plain pointers, not `const __restrict__`:
 // with programmatic dependent launch a kernel may start before its predecessor has finished, and
 // the non-coherent load path that `const __restrict__` selects could then return stale lines.
@@ -14,7 +15,7 @@ extern "C" int sb_abi_version() { return 1; }
 // fed back on the device) reads nothing and gives a row of NaN, which stays visible downstream.
 template <typename TW>
 __global__ void embed_kernel(const int32_t* tokens, const TW* __restrict__ table, int vocab,
-                             int width, float* __restrict__ out) {
+                             int width, float scale, float* __restrict__ out) {
   sb_pdl_launch();
   sb_pdl_wait();
   const int t = blockIdx.x;
@@ -25,16 +26,19 @@ __global__ void embed_kernel(const int32_t* tokens, const TW* __restrict__ table
     return;
   }
   const TW* row = table + (size_t)id * width;
-  for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = sb_to_f32<TW>(row[i]);
+  if (scale == 1.0f)
+    for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = sb_to_f32<TW>(row[i]);
+  else
+    for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = sb_to_f32<TW>(row[i]) * scale;
 }
 
 extern "C" int sb_embed(const int32_t* tokens, int n_rows, const void* table, int table_dtype,
-                        int vocab, int width, float* out, cudaStream_t stream) {
+                        int vocab, int width, float scale, float* out, cudaStream_t stream) {
   if (n_rows <= 0 || width <= 0 || vocab <= 0)
     SB_FAIL(SB_ERR_ARG, "sb_embed: n_rows=%d vocab=%d width=%d", n_rows, vocab, width);
   if (!sb_valid_dtype(table_dtype)) SB_FAIL(SB_ERR_ARG, "sb_embed: table dtype %d", table_dtype);
   SB_DISPATCH_DTYPE(table_dtype, TW, {
-    sb_launch<SB_K_ELEMENTWISE>(embed_kernel<TW>, dim3(n_rows), dim3(256), 0, stream, tokens, (const TW*)table, vocab, width, out);
+    sb_launch<SB_K_ELEMENTWISE>(embed_kernel<TW>, dim3(n_rows), dim3(256), 0, stream, tokens, (const TW*)table, vocab, width, scale, out);
   });
   SB_CHECK_LAUNCH("sb_embed");
   return SB_OK;
@@ -180,6 +184,27 @@ extern "C" int sb_rmsnorm(const float* x, const int32_t* rows, int n_rows, int w
   return SB_OK;
 }
 
+// --------------------------------------------------------------------------------- logit cap
+// x = cap * tanh(x / cap) in place (core/src/model/emit.cpp:520-522, the reference's Softcap op
+// on the logits; core/src/nn/sampling.cpp:229).  Not used by this architecture: a model whose
+// spec names a cap gets it here.
+__global__ void softcap_kernel(float* x, size_t n, float cap) {
+  sb_pdl_launch();
+  sb_pdl_wait();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (size_t)gridDim.x * blockDim.x)
+    x[i] = cap * tanhf(x[i] / cap);
+}
+
+extern "C" int sb_softcap(float* x, size_t n, float cap, cudaStream_t stream) {
+  if (!(cap > 0.0f)) SB_FAIL(SB_ERR_ARG, "sb_softcap: cap %g must be positive", cap);
+  if (n == 0) return SB_OK;
+  const int blocks = (int)((n + 255) / 256 < 4096 ? (n + 255) / 256 : 4096);
+  sb_launch<SB_K_ELEMENTWISE>(softcap_kernel, dim3(blocks), dim3(256), 0, stream, x, n, cap);
+  SB_CHECK_LAUNCH("sb_softcap");
+  return SB_OK;
+}
+
 // ------------------------------------------------------------------------------------ cast
 template <typename TI, typename TO>
 __global__ void cast_kernel(const TI* in, TO* out, size_t n) {
@@ -216,6 +241,16 @@ extern "C" int sb_cast(const void* in, int in_dtype, void* out, int out_dtype, s
 //
 // Cache of one schedule entry: [page][k|v][kv head][slot in page][hd].  The page of position p
 // of sequence b is page_ids[page_off[b] + p / page_size].
+// A row whose position has no page in its own sequence's list (a position before 0 or beyond
+// what the sequence has reserved, or a page that was given back) writes no key and no value:
+// another sequence's pages are never touched, whatever the plan says.
+__device__ __forceinline__ int sb_page_of(const int32_t* page_off, const int32_t* page_ids, int seq,
+                                          int pos, int page_size) {
+  const int first = page_off[seq], n = page_off[seq + 1] - first;
+  const int i = pos / page_size;
+  return (pos >= 0 && i < n) ? page_ids[first + i] : -1;
+}
+
 // Few rows (decode): one block per (row, head), so that even one row spreads over many SMs.
 template <typename TQ, typename TC>
 __global__ void rope_store_head_kernel(const float* qkv, int n_q_heads, int n_kv_heads, int hd,
@@ -236,7 +271,8 @@ __global__ void rope_store_head_kernel(const float* qkv, int n_q_heads, int n_kv
   const int pos = row_pos[t];
   size_t dst_row = 0;
   if (head >= n_q_heads) {
-    const int page = page_ids[page_off[row_seq[t]] + pos / page_size];
+    const int page = sb_page_of(page_off, page_ids, row_seq[t], pos, page_size);
+    if (page < 0) return;                            // no page of its own there: nothing is written
     const int kvh = is_v ? head - n_q_heads - n_kv_heads : head - n_q_heads;
     dst_row = (((size_t)page * 2 + (is_v ? 1 : 0)) * n_kv_heads + kvh) * page_size + pos % page_size;
   }
@@ -291,10 +327,12 @@ __global__ void rope_store_kernel(const float* qkv, int n_q_heads, int n_kv_head
   const int n_heads = n_q_heads + (has_kv ? 2 * n_kv_heads : 0);
   const float* src_row = qkv + (size_t)t * n_heads * hd;
   size_t k_base = 0, v_base = 0;
+  bool stores = has_kv;
   if (has_kv) {
-    const int page = page_ids[page_off[row_seq[t]] + pos / page_size];
-    k_base = (((size_t)page * 2) * n_kv_heads * page_size + pos % page_size) * hd;
-    v_base = (((size_t)page * 2 + 1) * n_kv_heads * page_size + pos % page_size) * hd;
+    const int page = sb_page_of(page_off, page_ids, row_seq[t], pos, page_size);
+    stores = page >= 0;                              // no page of its own there: queries only
+    k_base = (((size_t)(stores ? page : 0) * 2) * n_kv_heads * page_size + pos % page_size) * hd;
+    v_base = (((size_t)(stores ? page : 0) * 2 + 1) * n_kv_heads * page_size + pos % page_size) * hd;
   }
   for (int idx = threadIdx.x; idx < n_heads * hd; idx += blockDim.x) {
     const int head = idx / hd, e = idx % hd;       // q heads, then k heads, then v heads
@@ -308,6 +346,8 @@ __global__ void rope_store_kernel(const float* qkv, int n_q_heads, int n_kv_head
     }
     if (head < n_q_heads) {
       q_out[((size_t)t * n_q_heads + head) * hd + e] = sb_from_f32<TQ>(v);
+    } else if (!stores) {
+      continue;
     } else if (is_v) {
       cache[v_base + (size_t)(head - n_q_heads - n_kv_heads) * page_size * hd + e] = sb_from_f32<TC>(v);
     } else {
@@ -348,16 +388,19 @@ __global__ void rope_store_vec_kernel(const float* qkv, int n_q_heads, int n_kv_
   const int n_heads = n_q_heads + (has_kv ? 2 * n_kv_heads : 0);
   const float* src_row = qkv + (size_t)t * n_heads * hd;
   size_t k_base = 0, v_base = 0;
+  bool stores = has_kv;
   if (has_kv) {
-    const int page = page_ids[page_off[row_seq[t]] + pos / page_size];
-    k_base = (((size_t)page * 2) * n_kv_heads * page_size + pos % page_size) * hd;
-    v_base = (((size_t)page * 2 + 1) * n_kv_heads * page_size + pos % page_size) * hd;
+    const int page = sb_page_of(page_off, page_ids, row_seq[t], pos, page_size);
+    stores = page >= 0;                              // no page of its own there: queries only
+    k_base = (((size_t)(stores ? page : 0) * 2) * n_kv_heads * page_size + pos % page_size) * hd;
+    v_base = (((size_t)(stores ? page : 0) * 2 + 1) * n_kv_heads * page_size + pos % page_size) * hd;
   }
   const int pair_tasks = half >> 2, per_head = pair_tasks + ((hd - rot) >> 2);
   for (int task = threadIdx.x; task < n_heads * per_head; task += blockDim.x) {
     const int head = task / per_head, k = task % per_head;
     const float* src = src_row + (size_t)head * hd;
     const bool is_v = head >= n_q_heads + n_kv_heads;
+    if (head >= n_q_heads && !stores) continue;
     __nv_bfloat16* dst =
         head < n_q_heads ? q_out + ((size_t)t * n_q_heads + head) * hd
         : is_v ? cache + v_base + (size_t)(head - n_q_heads - n_kv_heads) * page_size * hd

@@ -298,7 +298,23 @@ __global__ void add_kernel(int32_t* x, int n, int delta) {
   if (i < n) x[i] += delta;
 }
 
+// x[i] = min(x[i] + 1, last[i]): a row of a captured decode batch moves to its next position
+// but never past the last position it holds pages for; a row that has finished stays there.
+__global__ void advance_kernel(int32_t* x, const int32_t* __restrict__ last, int n) {
+  sb_pdl_launch();
+  sb_pdl_wait();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) x[i] = min(x[i] + 1, last[i]);
+}
+
 }  // namespace
+
+extern "C" int sb_advance_rows(int32_t* x, const int32_t* last, int n, cudaStream_t stream) {
+  if (n <= 0 || !x || !last) SB_FAIL(SB_ERR_ARG, "sb_advance_rows: n=%d", n);
+  sb_launch(advance_kernel, dim3((n + 255) / 256), dim3(256), 0, stream, x, last, n);
+  SB_CHECK_LAUNCH("sb_advance_rows");
+  return SB_OK;
+}
 
 // x[i] += delta: advances the positions of a decode loop that stays on the device.
 extern "C" int sb_add_i32(int32_t* x, int n, int delta, cudaStream_t stream) {

@@ -41,16 +41,16 @@ class Engine:
     def free_slots(self) -> int:
         return self.cache.slots.free_count
 
-    def decode_loop(self, slots, max_new: int, samplings):
+    def decode_loop(self, slots, budgets, samplings):
         """The captured decode step for these live sequences, or None when it cannot serve
-        them: a windowed cache group gives pages back as it goes, and penalties need each
-        sequence's token history on the host."""
+        them (penalties need each sequence's token history on the host).  `budgets`: the most
+        tokens each of them will still be asked for; each gets pages for its own budget.  A
+        windowed cache group holds those pages for the life of the loop and gives back the
+        ones its window has left behind when the loop is closed."""
         from .decode import DecodeLoop
-        if not self.use_decode_loop or any(g.need.window > 0 for g in self.cache.groups):
+        if not self.use_decode_loop or any(s.penalizes for s in samplings):
             return None
-        if any(s.penalizes for s in samplings):
-            return None
-        return DecodeLoop(self, slots, max_new, samplings)
+        return DecodeLoop(self, slots, budgets, samplings)
 
     def step(self, entries) -> torch.Tensor:
         """entries: StepEntry items or (slot, tokens, want) tuples."""

@@ -59,78 +59,103 @@ def form_batch(pending: deque, free_pages: int, free_slots: int, page_size: int,
     return batch
 
 
+def _remaining(r: Request, results: list) -> int:
+    return r.sampling.max_tokens - len(results[r.index])
+
+
 def run_batch(engine, sampler, batch: list, results: list, on_token: Optional[Callable]) -> int:
-    """Runs one batch to its end; returns the number of steps it took."""
-    live = []                                    # (request, slot, history)
-    for r in batch:
-        live.append((r, engine.open(), list(r.prompt)))
-    logits = engine.step([(slot, r.prompt, [len(r.prompt) - 1]) for r, slot, _ in live])
-    steps = 1
-    tokens = sampler.sample(logits, [r.sampling for r, _, _ in live],
-                            [engine.length(slot) for _, slot, _ in live], [h for _, _, h in live])
-    while True:
-        still = []
-        for (r, slot, hist), tok in zip(live, tokens):
-            out = results[r.index]
-            out.append(tok)
-            hist.append(tok)
-            stop = tok in r.stop_tokens or len(out) >= r.sampling.max_tokens
-            if on_token is not None and on_token(r.index, tok):
-                stop = True
-            if stop:
-                engine.close(slot)               # slot and pages are free for the next batch
-            else:
-                still.append((r, slot, hist))
-        live = still
-        if not live:
-            return steps
-        make_loop = getattr(engine, "decode_loop", None)
-        loop = make_loop([slot for _, slot, _ in live],
-                         max(r.sampling.max_tokens - len(results[r.index]) for r, _, _ in live),
-                         [r.sampling for r, _, _ in live]) if make_loop else None
-        if loop is not None:
-            return steps + _run_device_loop(engine, loop, live, results, on_token)
-        logits = engine.step([(slot, [hist[-1]], [0]) for _, slot, hist in live])
-        steps += 1
+    """Runs one batch to its end; returns the number of steps it took.  Whatever happens, every
+    slot the batch opened has been closed when this returns or raises."""
+    held = set()                                 # slots this batch holds
+
+    def release(slot):
+        held.discard(slot)
+        engine.close(slot)                       # slot and pages are free for the next batch
+
+    try:
+        live = []                                # (request, slot, history)
+        for r in batch:
+            slot = engine.open()
+            held.add(slot)
+            live.append((r, slot, list(r.prompt)))
+        logits = engine.step([(slot, r.prompt, [len(r.prompt) - 1]) for r, slot, _ in live])
+        steps = 1
         tokens = sampler.sample(logits, [r.sampling for r, _, _ in live],
                                 [engine.length(slot) for _, slot, _ in live], [h for _, _, h in live])
+        while True:
+            still = []
+            for (r, slot, hist), tok in zip(live, tokens):
+                out = results[r.index]
+                out.append(tok)
+                hist.append(tok)
+                stop = tok in r.stop_tokens or len(out) >= r.sampling.max_tokens
+                if on_token is not None and on_token(r.index, tok):
+                    stop = True
+                if stop:
+                    release(slot)
+                else:
+                    still.append((r, slot, hist))
+            live = still
+            if not live:
+                return steps
+            make_loop = getattr(engine, "decode_loop", None)
+            loop = make_loop([slot for _, slot, _ in live], [_remaining(r, results) for r, _, _ in live],
+                             [r.sampling for r, _, _ in live]) if make_loop else None
+            if loop is not None:
+                return steps + _run_device_loop(engine, loop, live, results, on_token, release)
+            logits = engine.step([(slot, [hist[-1]], [0]) for _, slot, hist in live])
+            steps += 1
+            tokens = sampler.sample(logits, [r.sampling for r, _, _ in live],
+                                    [engine.length(slot) for _, slot, _ in live], [h for _, _, h in live])
+    finally:
+        for slot in sorted(held):
+            engine.close(slot)
 
 
-def _run_device_loop(engine, loop, live: list, results: list, on_token: Optional[Callable]) -> int:
+def _run_device_loop(engine, loop, live: list, results: list, on_token: Optional[Callable],
+                     release: Callable) -> int:
     """The rest of a batch on the engine's captured decode step: each step's token ids go in
-    from the host and the new ids come back.  A finished sequence stays in the captured batch
-    as a row nobody reads until fewer than half of the rows are live; then the step is captured
-    again for the live ones.  Finished sequences' slots are closed when that happens."""
+    from the host and the new ids come back.  A finished sequence is retired: it stays in the
+    captured batch as a row nobody reads, held inside its own pages by the loop, until fewer
+    than half of the rows are live; then the loop is closed, the finished sequences' slots are
+    released, and the step is captured again for the live ones with what each of them may still
+    produce.  The loop is closed on every way out."""
     steps = 0
     rows = list(live)                            # the captured batch, in row order
     done = [False] * len(rows)
-    while True:
-        new = loop.step_host([0 if d else hist[-1] for (_, _, hist), d in zip(rows, done)])
-        steps += 1
-        for i, ((r, slot, hist), tok) in enumerate(zip(rows, new)):
-            if done[i]:
-                continue
-            out = results[r.index]
-            out.append(tok)
-            hist.append(tok)
-            stop = tok in r.stop_tokens or len(out) >= r.sampling.max_tokens
-            if on_token is not None and on_token(r.index, tok):
-                stop = True
-            done[i] = stop
-        n_live = done.count(False)
-        if n_live == 0 or 2 * n_live <= len(rows):
+    try:
+        while True:
+            new = loop.step_host([0 if d else hist[-1] for (_, _, hist), d in zip(rows, done)])
+            steps += 1
+            for i, ((r, slot, hist), tok) in enumerate(zip(rows, new)):
+                if done[i]:
+                    continue
+                out = results[r.index]
+                out.append(tok)
+                hist.append(tok)
+                stop = tok in r.stop_tokens or len(out) >= r.sampling.max_tokens
+                if on_token is not None and on_token(r.index, tok):
+                    stop = True
+                if stop:
+                    done[i] = True
+                    loop.retire(i)
+            n_live = done.count(False)
+            if n_live == 0 or 2 * n_live <= len(rows):
+                closing, loop = loop, None
+                closing.close()
+                for (r, slot, hist), d in zip(rows, done):
+                    if d:
+                        release(slot)
+                rows = [x for x, d in zip(rows, done) if not d]
+                if not rows:
+                    return steps
+                done = [False] * len(rows)
+                loop = engine.decode_loop([slot for _, slot, _ in rows],
+                                          [_remaining(r, results) for r, _, _ in rows],
+                                          [r.sampling for r, _, _ in rows])
+    finally:
+        if loop is not None:
             loop.close()
-            for (r, slot, hist), d in zip(rows, done):
-                if d:
-                    engine.close(slot)
-            rows = [x for x, d in zip(rows, done) if not d]
-            if not rows:
-                return steps
-            done = [False] * len(rows)
-            loop = engine.decode_loop(
-                [slot for _, slot, _ in rows],
-                max(r.sampling.max_tokens - len(results[r.index]) for r, _, _ in rows),
-                [r.sampling for r, _, _ in rows])
 
 
 def _per_request_stops(stop_tokens, n: int) -> list:

@@ -16,6 +16,7 @@ from dataclasses import dataclass, field
 import numpy as np
 import torch
 
+from .. import ops
 from ..cache.kv import Cache
 
 
@@ -126,7 +127,8 @@ def step(model, cache: Cache, entries: list[StepEntry]) -> torch.Tensor:
     for e in entries:
         cache.reserve(e.slot, cache.length(e.slot) + len(e.tokens))
     plan = StepPlan(cache, entries, model.device)
-    logits = model.forward(plan, cache)
+    with ops.trace_range(f"step ({plan.n_rows} rows, {plan.n_seqs} sequences)"):
+        logits = model.forward(plan, cache)
     for e in entries:
         cache.advance(e.slot, cache.length(e.slot) + len(e.tokens))
     return logits

@@ -2,7 +2,9 @@
 
 One class serves every architecture that can be written as a `ModelSpec`; what differs
 between architectures is the spec, not this code.  Order as the reference's emitter walks a
-recipe (core/src/model/emit.cpp:237-247 embedding, 436-459 blocks, 512-523 head): the head
+recipe (core/src/model/emit.cpp:237-247 embedding with its optional scale, 436-459 blocks,
+512-523 head with its optional logit cap; both are fields of the spec, as the reference keeps
+them as traits, core/src/model/recipe.cpp:35-61): the head
 runs only on the rows whose logits are wanted (the reference takes the last row only,
 core/src/model/gemma4_plan.cpp:599-605), and a tied head reads the embedding matrix
 (core/src/model/exec.cpp:516-517).
@@ -72,7 +74,7 @@ class DecoderModel:
         [len(plan.want_rows), vocab] (None when no logits are wanted)."""
         s = self.spec
         x = torch.empty((plan.n_rows, s.width), dtype=torch.float32, device=self.device)
-        ops.embed(plan.tokens, self.embedding, x)
+        ops.embed(plan.tokens, self.embedding, x, s.embedding_scale)
         ctx = StepContext(plan=plan, cache=cache)
         for i, e in enumerate(s.schedule):
             ctx.entry = i
@@ -83,12 +85,14 @@ class DecoderModel:
             ctx.after_block_norm = nxt.input_norm() if nxt is not None else None
             # ... and its first weights can be asked into L2 meanwhile, if it would ask late
             ctx.after_block_weights = nxt.first_weights(plan.n_rows) if nxt is not None else None
-            x = self.blocks[e.layer].forward(x, ctx)
+            with ops.trace_range(f"entry {i} (layer {e.layer})"):
+                x = self.blocks[e.layer].forward(x, ctx)
         if plan.n_want == 0:
             return None
         hn = self.final_norm.forward(x, self.dtype, rows=plan.want_rows)
         logits = torch.empty((plan.n_want, s.vocab), dtype=torch.float32, device=self.device)
-        return ops.linear(hn, self.head, logits)
+        ops.linear(hn, self.head, logits)
+        return ops.softcap(logits, s.logit_cap) if s.logit_cap > 0.0 else logits
 
 
 def tensor_requests(spec: ModelSpec) -> list[TensorRequest]:

@@ -60,6 +60,37 @@ def _stream():
 LAUNCHES = 0          # kernels launched through this module so far (a running count)
 
 
+# Opt-in NVTX ranges around steps and schedule entries, in the manner of the reference's
+# SONICBOOM_NVTX switch (core/src/model/gemma4_plan.cpp:50, 87-91): SB_TRACE=1 in the
+# environment or `set_trace(True)`.  Off, `trace_range` hands out one shared no-op object.
+import contextlib as _contextlib
+import os as _os
+
+TRACE = _os.environ.get("SB_TRACE", "0") not in ("", "0")
+_NO_RANGE = _contextlib.nullcontext()
+
+
+def set_trace(on: bool) -> None:
+    global TRACE
+    TRACE = bool(on)
+
+
+class _Range:
+    def __init__(self, name):
+        self.name = name
+
+    def __enter__(self):
+        torch.cuda.nvtx.range_push(self.name)
+
+    def __exit__(self, *exc):
+        torch.cuda.nvtx.range_pop()
+
+
+def trace_range(name: str):
+    """A context manager that is an NVTX range when tracing is on, else nothing."""
+    return _Range(name) if TRACE else _NO_RANGE
+
+
 def _check(rc: int, what: str, launches: int = 1) -> None:
     global LAUNCHES
     if rc != 0:
@@ -73,13 +104,22 @@ def _i32(t, what):
     return _ptr(t)
 
 
-def embed(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """out[t] = table[tokens[t]] as float32; an id outside the table gives a row of NaN."""
+def embed(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor,
+          scale: float = 1.0) -> torch.Tensor:
+    """out[t] = table[tokens[t]] * scale as float32; an id outside the table gives a row of NaN."""
     n, width = tokens.numel(), table.shape[1]
     assert out.dtype == torch.float32 and out.shape == (n, width)
     _check(lib().sb_embed(_i32(tokens, "tokens"), n, _ptr(table), _code(table.dtype),
-                          table.shape[0], width, _ptr(out), _stream()), "embed")
+                          table.shape[0], width, ctypes.c_float(scale), _ptr(out), _stream()), "embed")
     return out
+
+
+def softcap(x: torch.Tensor, cap: float) -> torch.Tensor:
+    """x = cap * tanh(x / cap) in place (float32)."""
+    assert x.dtype == torch.float32 and x.is_contiguous()
+    _check(lib().sb_softcap(_ptr(x), ctypes.c_size_t(x.numel()), ctypes.c_float(cap), _stream()),
+           "softcap")
+    return x
 
 
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
@@ -201,7 +241,6 @@ def _warm_args(warm):
     return _ptr(warm), ctypes.c_size_t(warm.numel() * warm.element_size())
 
 
-import os as _os
 WARM = _os.environ.get("SB_WARM", "1") != "0"       # L2 hints on (SB_WARM=0: off, for measurements)
 FORCE_DECODE_KERNEL = None      # "skinny" or "tc5": overrides the choice below (for measurements)
 
@@ -398,15 +437,44 @@ def sample(logits: torch.Tensor, params: torch.Tensor, history: torch.Tensor | N
     return out_tokens
 
 
-def check_tokens(ids: list) -> list:
-    """Sampled ids as read on the host: raises where the sampler chose no token."""
-    bad = [i for i, t in enumerate(ids) if t < 0]
+def check_tokens(ids: list, live: list | None = None) -> list:
+    """Sampled ids as read on the host: raises where the sampler chose no token (rows whose
+    `live` entry is false are not looked at)."""
+    bad = [i for i, t in enumerate(ids) if t < 0 and (live is None or live[i])]
     if bad:
         raise KernelError(f"the sampler chose no token for row {bad[0]}: its logits are not finite")
     return ids
+
+
+def check_status() -> None:
+    """Raises KernelError if a kernel of any loaded library gave up on one of its bounded waits
+    since the last look (its output is then incomplete).  Reading synchronizes with the device,
+    so this is called where the host waits anyway."""
+    if _lib is None:
+        return
+    code = tc5_status()
+    if code:
+        raise KernelError(f"a tcgen05 product kernel gave up on a bounded wait (code {code}): "
+                          "results since the last check are incomplete")
+    for hd, l in _attn_libs.items():
+        if l is not None:
+            code = int(l.sb_attention_status())
+            if code > 0:
+                raise KernelError(f"the tensor-memory attention kernel of head size {hd} gave up "
+                                  f"on a bounded wait (code {code}): results since the last check "
+                                  "are incomplete")
 
 
 def add_i32(x: torch.Tensor, delta: int) -> torch.Tensor:
     """x += delta on the device (int32)."""
     _check(lib().sb_add_i32(_i32(x, "x"), x.numel(), int(delta), _stream()), "add_i32")
     return x
+
+
+def advance_rows(pos: torch.Tensor, last: torch.Tensor) -> torch.Tensor:
+    """pos[i] = min(pos[i] + 1, last[i]) on the device (int32): the positions of a captured
+    decode batch move on, each row at most to the last position it holds pages for."""
+    assert pos.numel() == last.numel()
+    _check(lib().sb_advance_rows(_i32(pos, "pos"), _i32(last, "last"), pos.numel(), _stream()),
+           "advance_rows")
+    return pos

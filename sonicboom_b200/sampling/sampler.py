@@ -53,4 +53,6 @@ class Sampler:
         hist = torch.from_numpy(history).to(self.device) if history is not None else None
         out = torch.empty(logits.shape[0], dtype=torch.int32, device=self.device)
         ops.sample(logits, params, hist, out)
-        return ops.check_tokens(out.cpu().tolist())
+        ids = out.cpu().tolist()
+        ops.check_status()           # the host has just waited for the step: a cheap place to look
+        return ops.check_tokens(ids)

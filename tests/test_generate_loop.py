@@ -192,3 +192,175 @@ def test_a_row_without_a_sampled_token_is_an_error():
     assert ops.check_tokens([3, 0, 7]) == [3, 0, 7]
     with pytest.raises(ops.KernelError, match="row 1"):
         ops.check_tokens([3, -1, 7])
+
+
+# ------------------------------------------------------------------ the captured decode loop
+class FakeLoop:
+    """Stands in for engine.decode.DecodeLoop with the same contract: per-row budgets and
+    reservations, positions that advance as the device kernel advances them (one step at a
+    time, never past the last reserved position), `retire`, and `close` recording what each
+    row was fed while live."""
+
+    def __init__(self, engine, slots, budgets, samplings):
+        assert len(slots) == len(budgets) == len(samplings) and min(budgets) >= 1
+        self.engine, self.slots, self.budgets = engine, list(slots), list(budgets)
+        self.start = [engine.lengths[s] for s in slots]
+        for s, at, b in zip(slots, self.start, budgets):
+            engine.reserved[s] = max(engine.reserved.get(s, 0), pages_for(at + b, 64))
+        assert engine.pages_out() <= engine.n_pages, "the loop reserved more than the cache holds"
+        self.pos = list(self.start)
+        self.last = [at + b - 1 for at, b in zip(self.start, budgets)]
+        self.live, self.fed, self.closed = [True] * len(slots), [0] * len(slots), False
+        self.positions_written = [[] for _ in slots]
+        engine.loops.append(self)
+
+    def retire(self, row):
+        assert self.live[row]
+        self.live[row] = False
+
+    def step_host(self, tokens):
+        assert not self.closed
+        out = []
+        for i, (slot, tok) in enumerate(zip(self.slots, tokens)):
+            # every row of the captured batch runs, live or not, and writes at its position
+            assert self.pos[i] <= self.last[i] < self.engine.reserved[slot] * 64
+            self.positions_written[i].append(self.pos[i])
+            if self.live[i]:
+                assert self.fed[i] < self.budgets[i], "a live row was stepped past its budget"
+                assert self.pos[i] == self.start[i] + self.fed[i]
+                self.engine.fed[slot].append(tok)
+                self.fed[i] += 1
+                out.append(sum(self.engine.fed[slot]) % 50)
+            else:
+                out.append(-1)                   # a retired row's id means nothing
+            self.pos[i] = min(self.pos[i] + 1, self.last[i])
+        self.engine.loop_steps.append(len(self.slots))
+        return out
+
+    def close(self):
+        assert not self.closed, "a loop was closed twice"
+        self.closed = True
+        for slot, at, fed in zip(self.slots, self.start, self.fed):
+            if slot in self.engine.lengths:
+                self.engine.lengths[slot] = at + fed
+
+
+class LoopEngine(FakeEngine):
+    """FakeEngine with a captured decode loop; pages are counted as the real cache counts them
+    (what a sequence holds or has reserved), and slots must be closed exactly once."""
+
+    def __init__(self, n_pages=64, n_slots=8):
+        super().__init__(n_pages, n_slots)
+        self.reserved, self.loops, self.loop_steps, self.closed_slots = {}, [], [], []
+
+    def pages_out(self):
+        return sum(max(pages_for(n, 64), self.reserved.get(s, 0)) for s, n in self.lengths.items())
+
+    def free_pages(self):
+        return self.n_pages - self.pages_out()
+
+    def close(self, slot):
+        assert slot in self.lengths, f"slot {slot} closed twice"
+        self.closed_slots.append(slot)
+        self.reserved.pop(slot, None)
+        super().close(slot)
+
+    def decode_loop(self, slots, budgets, samplings):
+        return FakeLoop(self, slots, budgets, samplings)
+
+
+def check_loops(eng):
+    assert not eng.lengths and sorted(eng.closed_slots) == sorted(eng.opened)   # each slot once
+    assert all(l.closed for l in eng.loops)
+    for l in eng.loops:
+        for written, last in zip(l.positions_written, l.last):
+            assert max(written) <= last
+
+
+def test_device_loop_with_per_request_budgets_in_batches_of_three_to_seven():
+    for n in range(3, 8):
+        eng, smp = LoopEngine(), FakeSampler()
+        prompts = [[i + 1] * (1 + 9 * i) for i in range(n)]
+        per = [Sampling(max_tokens=2 + 3 * ((i * 5) % 7)) for i in range(n)]
+        out = generate(eng, smp, prompts, per)
+        assert out == [expected(p, s.max_tokens) for p, s in zip(prompts, per)], n
+        check_loops(eng)
+        # the step is captured again once half of the rows (or more) have finished: never
+        # does a loop keep running with more than half of its rows retired
+        sizes = [len(l.slots) for l in eng.loops]
+        assert sizes[0] == n and all(2 * b <= a or b < a for a, b in zip(sizes, sizes[1:]))
+        assert len(eng.loops) >= 2
+
+
+def test_device_loop_recaptures_at_half():
+    eng, smp = LoopEngine(), FakeSampler()
+    prompts = [[1], [2], [3], [4]]
+    per = [Sampling(max_tokens=m) for m in (3, 9, 4, 9)]
+    out = generate(eng, smp, prompts, per)
+    assert [len(o) for o in out] == [3, 9, 4, 9]
+    check_loops(eng)
+    # first token from the prompt step; row 0 ends after 2 loop steps (3 of 4 live: no
+    # recapture), row 2 after 3 (2 of 4 live: recapture with the two live rows)
+    assert [len(l.slots) for l in eng.loops] == [4, 2]
+    assert eng.loop_steps == [4, 4, 4] + [2] * 5
+    assert eng.loops[0].fed == [2, 3, 3, 3] and eng.loops[1].budgets == [5, 5]
+
+
+def test_device_loop_stop_tokens_and_callback():
+    prompts = [[1, 2, 3], [10, 11], [7], [9, 9], [4, 4, 4]]
+    free = [expected(p, 12) for p in prompts]
+    stop = free[0][4]
+    eng = LoopEngine()
+    seen = []
+
+    def cb(i, tok):
+        seen.append((i, tok))
+        return i == 3 and sum(1 for j, _ in seen if j == 3) == 6
+    out = generate(eng, FakeSampler(), prompts, Sampling(max_tokens=12),
+                   stop_tokens=[[stop], [], [], [], []], on_token=cb)
+    assert out[0] == free[0][:5] and out[3] == free[3][:6]
+    assert out[1] == free[1] and out[2] == free[2] and out[4] == free[4]
+    assert [t for i, t in seen if i == 1] == out[1]
+    check_loops(eng)
+
+
+def test_device_loop_at_exactly_the_cache_form_batch_budgets():
+    """Two requests of 10 prompt tokens, one allowed 10 new tokens and one 1,000: 1 + 16 pages.
+    A loop that reserved the largest budget for every row would need 32."""
+    eng = LoopEngine(n_pages=17, n_slots=2)
+    prompts = [[1] * 10, [2] * 10]
+    per = [Sampling(max_tokens=10), Sampling(max_tokens=1000)]
+    out = generate(eng, FakeSampler(), prompts, per)
+    assert [len(o) for o in out] == [10, 1000] and out[0] == expected(prompts[0], 10)
+    check_loops(eng)
+    assert len(eng.opened) == 2 and len(set(eng.opened)) == 2        # one batch
+
+
+def test_slots_are_closed_when_a_step_fails():
+    class Boom(RuntimeError):
+        pass
+
+    class FailingLoop(FakeLoop):
+        def step_host(self, tokens):
+            if len(self.engine.loop_steps) == 2:
+                raise Boom("a kernel gave up")
+            return super().step_host(tokens)
+
+    class FailingEngine(LoopEngine):
+        def decode_loop(self, slots, budgets, samplings):
+            return FailingLoop(self, slots, budgets, samplings)
+
+    eng = FailingEngine()
+    with pytest.raises(Boom):
+        generate(eng, FakeSampler(), [[1], [2], [3]], Sampling(max_tokens=8))
+    assert not eng.lengths and sorted(eng.closed_slots) == sorted(eng.opened)
+    assert all(l.closed for l in eng.loops)
+
+    class FullEngine(LoopEngine):
+        def decode_loop(self, slots, budgets, samplings):
+            from sonicboom_b200.cache import CacheFull
+            raise CacheFull("no pages")
+    eng = FullEngine()
+    with pytest.raises(Exception, match="no pages"):
+        generate(eng, FakeSampler(), [[1], [2]], Sampling(max_tokens=8))
+    assert not eng.lengths and sorted(eng.closed_slots) == sorted(eng.opened)

@@ -107,6 +107,95 @@ def test_stop_tokens_and_eos(model_dirs, oracles, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_unequal_budgets_next_to_the_context_limit(model_dirs, oracles, dtype):
+    """Configuration A holds 128 positions.  Prompts of 100, 5 and 5 tokens that may produce 20,
+    100 and 100: the first request is finished after 20 tokens and stays a row of the captured
+    batch while the others go on for 80 more steps.  It must stay inside its own two pages:
+    the others' tokens are what they are alone, and what the plain implementation gives."""
+    model = llm.model_load(model_dirs["A"], dtype=dtype)
+    prompts = prompts_for("A", [100, 5, 5], seed=12)
+    per = [Sampling(max_tokens=m) for m in (20, 100, 100)]
+    outs = llm.generate_batch(model, prompts, sampling=per, ignore_eos=True)
+    assert [len(o) for o in outs] == [20, 100, 100]
+    scale = float(pm.forward(*oracles["A"], prompts[0]).abs().max())
+    for p, s, o in zip(prompts, per, outs):
+        alone = llm.generate_batch(model, [p], sampling=s, ignore_eos=True)[0]
+        want, margins = plain_tokens(oracles["A"], p, s.max_tokens)
+        if dtype == "float32":
+            assert o == alone == want
+        else:
+            assert_same_or_near_tie(o, want, margins, scale, dtype)
+            assert_same_or_near_tie(alone, want, margins, scale, dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_cache_of_exactly_what_the_batch_was_admitted_for(model_dirs, oracles, dtype):
+    """Four requests with budgets 3, 150, 4 and 40 in a cache of exactly the pages their prompts
+    and own budgets need (1 + 3 + 1 + 1): the captured loop reserves each row's own budget, is
+    captured again when half of the rows have finished, and the engine ends with every page and
+    slot free."""
+    from sonicboom_b200 import Engine
+    model = llm.model_load(model_dirs["B"], dtype=dtype)
+    prompts = prompts_for("B", [10, 12, 30, 7], seed=13)
+    per = [Sampling(max_tokens=m) for m in (3, 150, 4, 40)]
+    engine = Engine(model.decoder, max_tokens=64 * 6)
+    outs = llm.generate_batch(model, prompts, sampling=per, ignore_eos=True, engine=engine)
+    assert [len(o) for o in outs] == [3, 150, 4, 40]
+    engine.cache.check()
+    assert not engine.cache.records and engine.free_pages() == 6
+    scale = float(pm.forward(*oracles["B"], prompts[2]).abs().max())
+    for p, s, o in zip(prompts, per, outs):
+        want, margins = plain_tokens(oracles["B"], p, s.max_tokens)
+        if dtype == "float32":
+            assert o == want
+        else:
+            assert_same_or_near_tie(o, want, margins, scale, dtype)
+    # one page less and the batch is two batches; the tokens stay the same in float32
+    small = Engine(model.decoder, max_tokens=64 * 5)
+    again = llm.generate_batch(model, prompts, sampling=per, ignore_eos=True, engine=small)
+    if dtype == "float32":
+        assert again == outs
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_windowed_model_decodes_through_the_captured_loop(model_dirs, oracles, dtype, monkeypatch):
+    """Configuration C has layers with a window of 40 keys.  Its decode steps are captured like
+    any other model's: the windowed group holds its pages while the loop lives and gives back
+    the ones behind the window when the loop is closed.  Same tokens as step by step without
+    the captured loop, and as the plain implementation."""
+    from sonicboom_b200 import Engine
+    from sonicboom_b200.engine.decode import DecodeLoop
+    model = llm.model_load(model_dirs["C"], dtype=dtype)
+    made = []
+    real_init = DecodeLoop.__init__
+
+    def spy(self, *a, **k):
+        real_init(self, *a, **k)
+        made.append(self)
+    monkeypatch.setattr(DecodeLoop, "__init__", spy)
+    prompts = prompts_for("C", [3, 50, 70], seed=14)
+    per = [Sampling(max_tokens=m) for m in (90, 30, 100)]
+    engine = Engine(model.decoder, max_tokens=64 * 8)
+    outs = llm.generate_batch(model, prompts, sampling=per, ignore_eos=True, engine=engine)
+    assert made and any(g.need.window > 0 for g in engine.cache.groups)
+    engine.cache.check()
+    assert not engine.cache.records and engine.free_pages() == 8
+    stepwise = Engine(model.decoder, max_tokens=64 * 8)
+    stepwise.use_decode_loop = False
+    n_loops = len(made)
+    again = llm.generate_batch(model, prompts, sampling=per, ignore_eos=True, engine=stepwise)
+    assert len(made) == n_loops
+    scale = float(pm.forward(*oracles["C"], prompts[1]).abs().max())
+    for p, s, o, a in zip(prompts, per, outs, again):
+        want, margins = plain_tokens(oracles["C"], p, s.max_tokens)
+        if dtype == "float32":
+            assert o == a == want
+        else:
+            assert_same_or_near_tie(o, want, margins, scale, dtype)
+            assert_same_or_near_tie(a, want, margins, scale, dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_sampled_generation_matches_the_plain_sampler(model_dirs, oracles, dtype):
     model = llm.model_load(model_dirs["A"], dtype=dtype)
     prompts = prompts_for("A", [5, 11, 17], seed=7)

@@ -496,3 +496,66 @@ def test_sampled_tokens_do_not_depend_on_the_row():
     a = sampler.sample(logits, [s] * 4, [10, 11, 12, 13], [[]] * 4)
     b = sampler.sample(logits.flip(0).contiguous(), [s] * 4, [13, 12, 11, 10], [[]] * 4)
     assert a == b[::-1]
+
+
+# ------------------------------------------------ positions outside a sequence's own pages
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("hq,hkv,hd,rows", [(4, 2, 16, 3), (28, 4, 128, 3), (4, 2, 16, 80)])
+def test_a_position_without_a_page_of_its_own_writes_and_reads_nothing(dtype, hq, hkv, hd, rows):
+    """Rows whose position lies beyond their sequence's page list (a plan that a finished row of
+    a captured batch would reach if nothing stopped it), or before 0: the rotation kernel writes
+    no key or value for them, the attention gives them rows of zeros, every other sequence's
+    pages stay as they were, and the neighbours' results are what they are without them.  All
+    three forms of the rotation kernel (per head, per row, vector) and the decode attention's
+    merge counters are covered: a second, ordinary step right after gives the right result."""
+    dt = DT[dtype]
+    cache = make_cache(hkv, hd, 0, dt, max_tokens=64 * 7 * rows)
+    storage = cache.groups[0].entry_storage(0)
+    slots = [cache.open() for _ in range(rows)]
+    width = (hq + 2 * hkv) * hd
+    base = 300                                              # two key splits in the decode kernel
+    hist = [rnd(base + i, width, seed=30 + i).cpu() for i in range(rows)]
+    run_attention(cache, hq, hkv, hd, 0, dt, [(s, h) for s, h in zip(slots, hist)])
+    new = [rnd(1, width, seed=60 + i).cpu() for i in range(rows)]
+    for s in slots:
+        cache.reserve(s, cache.length(s) + 1)
+    plan = StepPlan(cache, [StepEntry(s, [0], []) for s in slots], DEV)
+    n_pg = [len(cache.page_list(s, 0)) for s in slots]
+    # the first and the last row: just beyond their own pages and far beyond; the second: before 0
+    bad = {0: 64 * n_pg[0], rows - 1: 64 * 2 * n_pg[-1] + 3, 1: -1}
+    pos = plan.row_pos.clone()
+    for r, p in bad.items():
+        pos[r] = p
+    plan.row_pos.copy_(pos)                                 # seq_pos0 is the same memory only in a decode plan
+    plan.seq_pos0.copy_(pos)
+    before = storage.clone()
+    qkv = torch.cat(new).to(DEV)
+    inv = torch.from_numpy(np.exp(-2.0 * np.arange(hd // 2, dtype=np.float32) / np.float32(hd)
+                                  * np.log(np.float32(10000.0))).astype(np.float32)).to(DEV)
+    q = torch.empty(rows, hq, hd, dtype=dt, device=DEV)
+    g = plan.groups[0]
+    ops.rope_store(qkv, hq, hkv, hd, hd, inv, plan.row_seq, plan.row_pos, g.page_off, g.page_ids,
+                   g.page_size, storage, q)
+    out = torch.full((rows, hq * hd), 7.0, dtype=dt, device=DEV)
+    ops.attention(q, out, plan, 0, storage, hq, hkv, hd, 0, hd ** -0.5)
+    torch.cuda.synchronize()
+    changed = (storage != before).any(dim=-1).any(dim=-1)             # [page, k|v, head]
+    good_pages = {cache.page_list(s, 0)[(base + i) // 64] for i, s in enumerate(slots) if i not in bad}
+    assert set(changed.nonzero()[:, 0].tolist()) == good_pages
+    out = out.float().cpu()
+    for r in range(rows):
+        if r in bad:
+            assert float(out[r].abs().max()) == 0.0
+        else:
+            ref = attention_ref(new[r], base + r, hq, hkv, hd, 0, history=hist[r])
+            close(out[r:r + 1], ref, 1e-5 if dtype == "float32" else 2e-2)
+    # the same step with its true positions right after: scratch and counters are as they should be
+    plan2 = StepPlan(cache, [StepEntry(s, [0], []) for s in slots], DEV)
+    g2 = plan2.groups[0]
+    ops.rope_store(qkv, hq, hkv, hd, hd, inv, plan2.row_seq, plan2.row_pos, g2.page_off, g2.page_ids,
+                   g2.page_size, storage, q)
+    out2 = torch.empty(rows, hq * hd, dtype=dt, device=DEV)
+    ops.attention(q, out2, plan2, 0, storage, hq, hkv, hd, 0, hd ** -0.5)
+    for r in range(rows):
+        ref = attention_ref(new[r], base + r, hq, hkv, hd, 0, history=hist[r])
+        close(out2[r:r + 1].float().cpu(), ref, 1e-5 if dtype == "float32" else 2e-2)

@@ -136,6 +136,15 @@ class RunningMean(parts.Mixer):
     def forward(self, h, ctx, residual=None):
         d = self.spec.width
         state = ctx.state()
+        if ctx.plan.n_rows == ctx.plan.n_seqs:
+            # one row per sequence (decoding): device work only, so that the step can be
+            # captured in a CUDA graph
+            slots_dev = ctx.plan.seq_slot.long()
+            sums = state[slots_dev, :d] + h.float()
+            count = state[slots_dev, d] + 1.0
+            state[slots_dev, :d], state[slots_dev, d] = sums, count
+            out = (sums / count[:, None]) @ self.w.t()
+            return out + residual if residual is not None else out
         row0 = ctx.plan.seq_row0.cpu().tolist()
         slots = ctx.plan.seq_slot.cpu().tolist()
         out = torch.empty(h.shape[0], d, dtype=torch.float32, device=h.device)
@@ -166,7 +175,7 @@ def toy_spec(width=48, vocab=97, n_layers=3):
                      NormSpec("rmsnorm", width, 1e-5, "toy.norm.weight"), None)
 
 
-def toy_reference(tensors, spec, tokens):
+def toy_reference(tensors, spec, tokens, head=None):
     """Whole-sequence forward of the toy model from plain parts."""
     t = {k: v.float().cpu() for k, v in tensors.items()}
     n = len(tokens)
@@ -188,7 +197,12 @@ def toy_reference(tensors, spec, tokens):
         f = pm.rms_norm(x, t[p + "n2.weight"], 1e-5)
         x = x + pm.swiglu_mlp(f, t[p + "mlp.gate_proj.weight"], t[p + "mlp.up_proj.weight"],
                               t[p + "mlp.down_proj.weight"])
-    return pm.linear(pm.rms_norm(x, t["toy.norm.weight"], 1e-5), t["toy.embed.weight"])
+    head = t["toy.embed.weight"] if head is None else head.float().cpu()
+    return pm.linear(pm.rms_norm(x, t["toy.norm.weight"], 1e-5), head)
+
+
+def toy_reference_with_head(tensors, spec, tokens, head):
+    return toy_reference(tensors, spec, tokens, head=head)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -221,6 +235,109 @@ def test_a_toy_mixer_with_state_registers_builds_and_steps(dtype):
                 eng.close(s)
     finally:
         parts.MIXERS.pop("running_mean")
+
+
+def toy_greedy(tensors, spec, prompt, n, reference=toy_reference):
+    seq, out = list(prompt), []
+    for _ in range(n):
+        tok = int(reference(tensors, spec, seq)[-1].argmax())
+        out.append(tok)
+        seq.append(tok)
+    return out
+
+
+def test_a_toy_mixer_with_state_generates_through_the_captured_loop(monkeypatch):
+    """The same toy model through the Python entry point with the captured decode step: the loop's
+    set-up run must leave the sequences' state as it found it, finished rows must not disturb
+    the others, and slots that are used again start from zeroed state.  Tokens in float32 are
+    those of the whole-sequence reference."""
+    from sonicboom_b200 import llm
+    from sonicboom_b200.engine.decode import DecodeLoop
+    parts.register_mixer("running_mean", RunningMean)
+    try:
+        spec = toy_spec()
+        model = DecoderModel(spec, torch.float32, DEV)
+        src = RandomSource(model.tensor_requests(), seed=4, std=0.08, bias_std=0.05, norm_std=0.1)
+        tensors = {n: src.tensor(n) for n in src.names()}
+        model.bind(lambda n: fetch(src, n, model.dtype, model.device))
+        made = []
+        real_init = DecodeLoop.__init__
+
+        def spy(self, *a, **k):
+            real_init(self, *a, **k)
+            made.append(self)
+        monkeypatch.setattr(DecodeLoop, "__init__", spy)
+        g = torch.Generator().manual_seed(1)
+        prompts = [torch.randint(0, 97, (n,), generator=g).tolist() for n in (9, 30, 4, 17)]
+        budgets = [12, 3, 20, 8]
+        eng = sb.Engine(model, max_tokens=64 * 4, n_slots=4)
+        from sonicboom_b200.sampling import Sampling
+        for round_ in range(2):                    # the second round uses the slots again
+            outs = llm.generate_batch(llm.Model(model), prompts, sampling=[Sampling(max_tokens=b) for b in budgets],
+                                      ignore_eos=True, engine=eng)
+            for p, b, o in zip(prompts, budgets, outs):
+                assert o == toy_greedy(tensors, spec, p, b), (round_, len(p))
+        assert len(made) >= 2 and all(l.graph is None for l in made)     # captured, then closed
+        eng.cache.check()
+        assert not eng.cache.records
+    finally:
+        parts.MIXERS.pop("running_mean")
+
+
+# -------------------------- a toy architecture with an embedding scale and a logit cap
+
+def test_a_toy_architecture_with_embedding_scale_and_logit_cap(tmp_path):
+    """Registered from here, written as a model folder, loaded by name from its config.json and
+    generated from: the embedding scale and the logit cap are fields of the model record, so
+    nothing in the package changes for an architecture that has them."""
+    import json
+    from sonicboom_b200 import llm
+    from sonicboom_b200.config import ARCHITECTURES, register_architecture
+
+    def to_spec(cfg):
+        base = toy_spec(cfg["width"], cfg["vocab"], cfg["layers"])
+        layers = tuple(dataclasses.replace(l, mixer=dataclasses.replace(base.layers[0].mixer,
+                                                                        prefix=f"toy.layers.{i}.self_attn."))
+                       for i, l in enumerate(base.layers))                # attention in every layer
+        return dataclasses.replace(base, architecture="ToyCappedForCausalLM", layers=layers,
+                                   embedding_scale=float(cfg["embedding_scale"]),
+                                   logit_cap=float(cfg["logit_cap"]))
+
+    def reference(tensors, spec, tokens):
+        t = dict(tensors)
+        t["toy.embed.weight"] = tensors["toy.embed.weight"].float() * spec.embedding_scale
+        # the head is the unscaled embedding matrix
+        plain = dataclasses.replace(spec, embedding_scale=1.0, logit_cap=0.0)
+        x_logits = toy_reference_with_head(t, plain, tokens, tensors["toy.embed.weight"])
+        return spec.logit_cap * torch.tanh(x_logits / spec.logit_cap)
+
+    register_architecture("ToyCappedForCausalLM", dict, to_spec)
+    try:
+        cfg = dict(architectures=["ToyCappedForCausalLM"], width=48, vocab=97, layers=2,
+                   embedding_scale=48 ** 0.5, logit_cap=3.0)
+        sb.write_random_model(tmp_path, cfg, seed=9, std=0.1, bias_std=0.05, norm_std=0.1)
+        assert json.loads((tmp_path / "config.json").read_text())["logit_cap"] == 3.0
+        tensors = pm.read_safetensors(tmp_path / "model.safetensors")
+        model = llm.model_load(tmp_path, dtype="float32")
+        assert model.arch == "ToyCappedForCausalLM"
+        spec = model.decoder.spec
+        g = torch.Generator().manual_seed(2)
+        prompts = [torch.randint(0, 97, (n,), generator=g).tolist() for n in (5, 21)]
+        eng = sb.Engine(model.decoder, max_tokens=256)
+        for p in prompts:
+            s = eng.open()
+            got = eng.step([(s, p, list(range(len(p))))]).cpu()
+            eng.close(s)
+            ref = reference(tensors, spec, p)
+            assert float(ref.abs().max()) > 0.5 * spec.logit_cap       # the cap really bends them
+            assert pm.rel_err(got, ref) < FP32_TOL
+        outs = llm.generate_batch(model, prompts, max_tokens=6, ignore_eos=True)
+        for p, o in zip(prompts, outs):
+            assert o == toy_greedy(tensors, spec, p, 6, reference)
+        with pytest.raises(sb.ConfigError, match="logit_cap"):
+            dataclasses.replace(spec, logit_cap=-1.0).validate()
+    finally:
+        ARCHITECTURES.pop("ToyCappedForCausalLM")
 
 
 # --------------------------- a toy feed-forward with routing and a toy position encoding
