@@ -478,3 +478,13 @@ def advance_rows(pos: torch.Tensor, last: torch.Tensor) -> torch.Tensor:
     _check(lib().sb_advance_rows(_i32(pos, "pos"), _i32(last, "last"), pos.numel(), _stream()),
            "advance_rows")
     return pos
+
+
+def random_normal(out: torch.Tensor, key0: int, key1: int, mean: float, std: float) -> torch.Tensor:
+    """Fills `out` (float32 or bfloat16, contiguous) with mean + std * z, z standard normal drawn
+    from the counter-based generator keyed by (key0, key1) and the element index."""
+    _check(lib().sb_random_normal(_ptr(out), _code(out.dtype), ctypes.c_size_t(out.numel()),
+                                  ctypes.c_uint32(key0 & 0xffffffff), ctypes.c_uint32(key1 & 0xffffffff),
+                                  ctypes.c_float(mean), ctypes.c_float(std), _stream()),
+           "random_normal")
+    return out

@@ -12,7 +12,7 @@ ROOT = Path(__file__).resolve().parent.parent
 sys.path.insert(0, str(ROOT))
 sys.path.insert(0, str(Path(__file__).resolve().parent))
 
-# Three tiny configurations of the architecture that differ in every size and option:
+# Four tiny configurations of the architecture that differ in every size and option:
 # layers, width, heads and groups (2:1, 6:1, 1:1), head size (16; 64 and 48 with an explicit
 # head_dim that is not width/heads; 64 runs the tensor-memory attention kernel), intermediate size, vocabulary (none a power of two in B
 # and C), rope base, norm eps, tied or separate head, and full or windowed attention.
@@ -27,6 +27,12 @@ TINY = {
               intermediate_size=512, vocab_size=1000, rope_theta=1000000.0, rms_norm_eps=1e-5,
               tie_word_embeddings=False, use_sliding_window=False, max_position_embeddings=256,
               eos_token_id=[998, 999]),
+    # D: the 3-layer configuration with its head size left to the rule width / heads = 32 and
+    # one key/value head for six query heads (B gives head_dim explicitly, 64)
+    "D": dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", hidden_size=192,
+              num_hidden_layers=3, num_attention_heads=6, num_key_value_heads=1,
+              intermediate_size=512, vocab_size=1000, rope_theta=1000000.0, rms_norm_eps=1e-5,
+              tie_word_embeddings=False, use_sliding_window=False, max_position_embeddings=256),
     "C": dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", hidden_size=200,
               num_hidden_layers=4, num_attention_heads=5, num_key_value_heads=5, head_dim=48,
               intermediate_size=136, vocab_size=1003, rope_theta=50000.0, rms_norm_eps=3e-5,
@@ -35,10 +41,36 @@ TINY = {
 }
 INIT = {"A": dict(std=0.02, bias_std=0.02, norm_std=0.05),
         "B": dict(std=0.03, bias_std=0.1, norm_std=0.1),
-        "C": dict(std=0.05, bias_std=0.1, norm_std=0.1)}
+        "C": dict(std=0.05, bias_std=0.1, norm_std=0.1),
+        "D": dict(std=0.03, bias_std=0.1, norm_std=0.1)}
 
-FP32_TOL = 1e-5      # largest |difference| / largest |reference logit|, float32 path vs oracle
-BF16_TOL = 2e-2      # same measure, bfloat16 path vs oracle
+# Tolerances: largest |difference| / largest |reference logit| over a request's logits.
+FP32_TOL = 1e-5      # the float32 path against the plain implementation
+# The bfloat16 path against the plain implementation (for "7B": against the engine's own
+# float32 path), per configuration: about three times the largest error the GPU tests measure
+# (they print what they measured at the end of a run).
+BF16_TOLS = {"A": 2e-2, "B": 2e-2, "C": 2e-2, "D": 2e-2, "7B": 2e-2}
+BF16_TOL = 2e-2      # where no configuration is at hand (parts and kernels alone, near ties)
+OBSERVED: dict = {}  # (configuration, dtype) -> largest error seen in this run
+
+
+def tol(name: str, dtype: str) -> float:
+    return FP32_TOL if dtype == "float32" else BF16_TOLS[name]
+
+
+def check_err(name: str, dtype: str, err: float, what: str = "") -> None:
+    """Records the error under its configuration and holds it against the tolerance."""
+    err = float(err)
+    key = (name, dtype)
+    OBSERVED[key] = max(OBSERVED.get(key, 0.0), err)
+    assert err < tol(name, dtype), f"{name} {dtype} {what}: error {err:.3g}, tolerance {tol(name, dtype):.3g}"
+
+
+def pytest_terminal_summary(terminalreporter):
+    if OBSERVED:
+        terminalreporter.write_line("largest logit errors measured (configuration, dtype: error / tolerance)")
+        for (name, dtype), err in sorted(OBSERVED.items()):
+            terminalreporter.write_line(f"  {name:>3} {dtype:>8}: {err:.3e} / {tol(name, dtype):.1e}")
 
 
 def pytest_configure(config):

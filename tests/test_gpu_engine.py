@@ -6,12 +6,13 @@ import pytest
 import torch
 
 import plain_model as pm
-from conftest import BF16_TOL, FP32_TOL, TINY, prompts_for
+from conftest import BF16_TOL, FP32_TOL, TINY, check_err, prompts_for, tol
 from gpu_util import batch_unequal, engine_for, oracle_logits, tail_one_by_one, whole
 
 pytestmark = pytest.mark.gpu
 TOL = {"float32": FP32_TOL, "bfloat16": BF16_TOL}
-LENGTHS = {"A": [5, 11, 17, 90], "B": [1, 7, 33, 64, 100], "C": [3, 40, 41, 65, 130, 200]}
+LENGTHS = {"A": [5, 11, 17, 90], "B": [1, 7, 33, 64, 100], "C": [3, 40, 41, 65, 130, 200],
+           "D": [1, 7, 33, 64, 100]}
 CASES = [(n, d) for n in TINY for d in ("float32", "bfloat16")]
 
 
@@ -19,8 +20,7 @@ CASES = [(n, d) for n in TINY for d in ("float32", "bfloat16")]
 def test_each_request_alone_and_whole(model_dirs, oracles, name, dtype):
     eng = engine_for(model_dirs, name, dtype)
     for p in prompts_for(name, LENGTHS[name]):
-        err = pm.rel_err(whole(eng, p), oracle_logits(oracles, name, p))
-        assert err < TOL[dtype], f"{name} {dtype} length {len(p)}: {err}"
+        check_err(name, dtype, pm.rel_err(whole(eng, p), oracle_logits(oracles, name, p)), f"whole, length {len(p)}")
     eng.cache.check()
 
 
@@ -30,8 +30,7 @@ def test_last_32_tokens_one_by_one(model_dirs, oracles, name, dtype):
     for p in prompts_for(name, [33, LENGTHS[name][-1]], seed=1):
         ref = oracle_logits(oracles, name, p)
         got = tail_one_by_one(eng, p, 32)
-        err = pm.rel_err(got, ref)
-        assert err < TOL[dtype], f"{name} {dtype} length {len(p)}: {err}"
+        check_err(name, dtype, pm.rel_err(got, ref), f"last 32 one by one, length {len(p)}")
         if dtype == "float32":     # cutting changes nothing beyond rounding
             assert pm.rel_err(got, whole(eng, p)) < FP32_TOL
 
@@ -49,8 +48,8 @@ def test_unequal_batches_one_after_another(model_dirs, oracles, name, dtype):
         got = batch_unequal(eng, reqs, prompt_lens)
         assert not eng.cache.records and before == set()
         for r, g in zip(reqs, got):
-            err = pm.rel_err(g, oracle_logits(oracles, name, r))
-            assert err < TOL[dtype], f"{name} {dtype} round {round_} length {len(r)}: {err}"
+            check_err(name, dtype, pm.rel_err(g, oracle_logits(oracles, name, r)),
+                      f"unequal batch, round {round_}, length {len(r)}")
         eng.cache.check()
     assert all(g.pool.free_count == g.pool.n for g in eng.cache.groups)
 
@@ -61,12 +60,11 @@ def test_long_decoding(model_dirs, oracles, name, dtype):
     eng = engine_for(model_dirs, name, dtype)
     (p,) = prompts_for(name, [n], seed=2)
     got = tail_one_by_one(eng, p, n - 4)           # 4 prompt tokens, everything else decoded
-    err = pm.rel_err(got, oracle_logits(oracles, name, p))
-    assert err < TOL[dtype], f"{name} {dtype}: {err}"
+    check_err(name, dtype, pm.rel_err(got, oracle_logits(oracles, name, p)), "long decoding")
     # the worst single position, to show where an error would sit (page edges: 64, 128, ...)
     ref = oracle_logits(oracles, name, p)
     per_pos = (got - ref).abs().amax(dim=1) / ref.abs().max()
-    assert float(per_pos.max()) < TOL[dtype], f"worst position {int(per_pos.argmax())}"
+    assert float(per_pos.max()) < tol(name, dtype), f"worst position {int(per_pos.argmax())}"
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -86,7 +84,7 @@ def test_a_long_context(tmp_path, dtype):
     for r, g in zip(reqs, got):
         ref = pm.forward(cfg, tensors, r)
         per_pos = (g - ref).abs().amax(dim=1) / ref.abs().max()
-        assert float(per_pos.max()) < TOL[dtype], f"{len(r)}: worst position {int(per_pos.argmax())}"
+        check_err("B", dtype, per_pos.max(), f"long context, length {len(r)}, worst position {int(per_pos.argmax())}")
     from sonicboom_b200 import ops
     assert ops.tc5_status() == 0 and ops.attention_status(TINY["B"]["head_dim"]) == 0
 
@@ -130,8 +128,8 @@ def test_first_tokens_of_a_sequence(model_dirs, oracles, name, dtype):
     got = batch_unequal(eng, reqs, [1, 2, 1])       # decoding starts right after the first token
     for r, g in zip(reqs, got):
         ref = oracle_logits(oracles, name, r)
-        assert pm.rel_err(g, ref) < TOL[dtype]
-        assert pm.rel_err(g[:2], ref[:2]) < TOL[dtype] * float(ref.abs().max() / ref[:2].abs().max())
+        check_err(name, dtype, pm.rel_err(g, ref), "first tokens")
+        assert pm.rel_err(g[:2], ref[:2]) < tol(name, dtype) * float(ref.abs().max() / ref[:2].abs().max())
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -143,7 +141,7 @@ def test_batch_position_and_neighbours_do_not_matter(model_dirs, dtype):
     for order in ([0, 1, 2], [2, 0, 1], [1, 2, 0]):
         got = batch_unequal(eng, [reqs[i] for i in order], [len(reqs[i]) for i in order])
         for i, g in zip(order, got):
-            assert pm.rel_err(g, alone[i]) < (1e-6 if dtype == "float32" else BF16_TOL), (order, i)
+            assert pm.rel_err(g, alone[i]) < (1e-6 if dtype == "float32" else tol("B", dtype)), (order, i)
 
 
 def test_refusals_reach_the_caller(model_dirs):
@@ -160,6 +158,83 @@ def test_refusals_reach_the_caller(model_dirs):
     with pytest.raises(CacheFull):
         eng.step([(t, [1] * 10, [])])
     assert eng.step([(s, [2], [])]) is None
+
+
+# --------------------------------------------------- two layers with the sizes of a 7B model
+BIG = dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", hidden_size=3584,
+           num_hidden_layers=2, num_attention_heads=28, num_key_value_heads=4,
+           intermediate_size=18944, vocab_size=8192, rope_theta=1000000.0, rms_norm_eps=1e-6,
+           max_position_embeddings=16384, tie_word_embeddings=False)
+BIG_INIT = dict(std=0.02, bias_std=0.02, norm_std=0.05)
+BIG_SEED = 3
+
+
+@pytest.fixture(scope="module")
+def big_models():
+    """The same seeded weights as a float32 and as a bfloat16 model (the random tensors are a
+    function of seed, name and index, rounded to bfloat16 before either model sees them)."""
+    import sonicboom_b200 as sb
+    models = {d: sb.random_model(BIG, BIG_SEED, dtype=d, device="cuda:0", **BIG_INIT)
+              for d in ("float32", "bfloat16")}
+    yield models
+    models.clear()
+    torch.cuda.empty_cache()
+
+
+def big_requests(lengths, seed):
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randint(0, BIG["vocab_size"], (n,), generator=g).tolist() for n in lengths]
+
+
+def test_float32_path_against_the_plain_implementation_at_7b_layer_sizes(big_models):
+    """Width 3,584, 28/4 heads of 128, intermediate 18,944: the true 32-bit path against the
+    plain implementation on a 256-token request (whole, and with its last 32 tokens one by
+    one), on the same random tensors, which the plain side gets from the generator's device
+    form copied to the host."""
+    import sonicboom_b200 as sb
+    from sonicboom_b200.models import tensor_requests
+    from sonicboom_b200.weights import RandomSource
+    src = RandomSource(tensor_requests(big_models["float32"].spec), BIG_SEED, device="cuda:0", **BIG_INIT)
+    tensors = {n: src.tensor(n).float().cpu() for n in src.names()}
+    (req,) = big_requests([256], seed=5)
+    ref = pm.forward(BIG, tensors, req)
+    eng = sb.Engine(big_models["float32"], max_tokens=512)
+    check_err("7B", "float32", pm.rel_err(whole(eng, req), ref), "whole, 256 tokens")
+    check_err("7B", "float32", pm.rel_err(tail_one_by_one(eng, req, 32), ref), "last 32 one by one")
+
+
+def test_bfloat16_path_against_the_float32_path_at_7b_layer_sizes(big_models):
+    """The serving path (tcgen05 products, tensor-memory and split attention, fused norms)
+    against the engine's own float32 path on the same weights: a request whole, with its last
+    32 tokens one by one, and in an unequal batch of three whose shorter requests end earlier.
+    The three cuts of the bfloat16 path are also held against each other."""
+    import sonicboom_b200 as sb
+    from sonicboom_b200 import ops
+    e32 = sb.Engine(big_models["float32"], max_tokens=4096)
+    e16 = sb.Engine(big_models["bfloat16"], max_tokens=4096)
+    reqs = big_requests([1100, 300, 70], seed=6)
+    tail = 32
+    want = lambda r: list(range(len(r) - tail, len(r)))     # the last 32 positions' logits
+
+    def whole_tail(eng, r):
+        s = eng.open()
+        out = eng.step([(s, r, want(r))]).float().cpu()
+        eng.close(s)
+        return out
+
+    refs = [whole_tail(e32, r) for r in reqs]
+    for r, ref in zip(reqs, refs):
+        check_err("7B", "bfloat16", pm.rel_err(whole_tail(e16, r), ref), f"whole, length {len(r)}")
+        got = tail_one_by_one(e16, r, tail)[-tail:]
+        check_err("7B", "bfloat16", pm.rel_err(got, ref), f"last 32 one by one, length {len(r)}")
+    got = batch_unequal(e16, reqs, [len(r) - tail - 5 * i for i, r in enumerate(reqs)])
+    for r, g, ref in zip(reqs, got, refs):
+        check_err("7B", "bfloat16", pm.rel_err(g[-tail:], ref), f"unequal batch, length {len(r)}")
+    # and the float32 path's own cuts agree with each other far more closely
+    got32 = batch_unequal(e32, reqs[1:], [len(r) - tail for r in reqs[1:]])
+    for g, ref in zip(got32, refs[1:]):
+        check_err("7B", "float32", pm.rel_err(g[-tail:], ref), "float32 cuts against each other")
+    assert ops.tc5_status() == 0 and ops.attention_status(128) == 0
 
 
 def test_layers_of_a_7b_model_decode_as_they_prefill():

@@ -12,7 +12,7 @@ import torch
 
 import plain_model as pm
 import plain_sampling as ps
-from conftest import BF16_TOL, FP32_TOL, ROOT, TINY, prompts_for
+from conftest import BF16_TOL, FP32_TOL, ROOT, TINY, check_err, prompts_for
 from sonicboom_b200 import llm
 from sonicboom_b200.sampling import Sampling
 
@@ -54,8 +54,8 @@ def assert_same_or_near_tie(got, want, margins, scale, dtype):
 def test_greedy_generation_of_a_batch(model_dirs, oracles, name, dtype):
     model = llm.model_load(model_dirs[name], dtype=dtype)
     assert model.arch == "Qwen2ForCausalLM" and model.vocab_size == TINY[name]["vocab_size"]
-    lens = {"A": [5, 11, 17], "B": [1, 7, 33, 64, 100], "C": [3, 50, 70]}[name]
-    n_new = {"A": 8, "B": 16, "C": 12}[name]
+    lens = {"A": [5, 11, 17], "B": [1, 7, 33, 64, 100], "C": [3, 50, 70], "D": [1, 7, 33, 64, 100]}[name]
+    n_new = {"A": 8, "B": 16, "C": 12, "D": 16}[name]
     prompts = prompts_for(name, lens, seed=5)
     outs = llm.generate_batch(model, prompts, max_tokens=n_new, ignore_eos=True)
     scale = float(pm.forward(*oracles[name], prompts[0]).abs().max())
@@ -277,7 +277,7 @@ def replay(model_dir, dtype, steps, out_dir, max_tokens):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["B", "C"])
+@pytest.mark.parametrize("name", ["B", "C", "D"])
 def test_trace_replay_three_cuts(model_dirs, oracles, tmp_path, name, dtype):
     vocab = TINY[name]["vocab_size"]
     reqs = {f"r{i}": p for i, p in enumerate(prompts_for(name, [100, 40, 70], seed=11))}
@@ -329,4 +329,13 @@ def test_trace_replay_three_cuts(model_dirs, oracles, tmp_path, name, dtype):
     for step_no, ref in expect.items():
         g = got[step_no].reshape(-1, vocab)
         assert g.shape == ref.shape, step_no
-        assert float(np.abs(g - ref).max()) / scale < TOL[dtype], step_no
+        check_err(name, dtype, float(np.abs(g - ref).max()) / scale, f"replay step {step_no}")
+    # the index beside the logits names the request and the position of every row written
+    index = [json.loads(l) for l in (tmp_path / "out" / "index.jsonl").read_text().splitlines()]
+    assert [r["step"] for r in index] == sorted(expect)
+    by_step = {r["step"]: r["rows"] for r in index}
+    assert by_step[0] == [["r0", i] for i in range(len(reqs["r0"]))]
+    last = max(expect)
+    assert len(by_step[last]) == expect[last].shape[0] and all(len(r) == 2 for r in by_step[last])
+    first_decode = len(reqs) + 1                  # the step after request r0's prefix step
+    assert by_step[first_decode] == [["r0x", len(reqs["r0"]) - 32]]

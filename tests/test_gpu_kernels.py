@@ -559,3 +559,44 @@ def test_a_position_without_a_page_of_its_own_writes_and_reads_nothing(dtype, hq
     for r in range(rows):
         ref = attention_ref(new[r], base + r, hq, hkv, hd, 0, history=hist[r])
         close(out2[r:r + 1].float().cpu(), ref, 1e-5 if dtype == "float32" else 2e-2)
+
+
+# ------------------------------------------------------------------ seeded random tensors
+@pytest.mark.parametrize("n", [1, 3, 4, 5, 257, 1_000_003])
+def test_random_tensors_are_the_same_bits_on_the_device_and_in_numpy(n):
+    """The kernel restates weights/random_init.normal_numpy step for step with individually
+    rounded float32 operations: float32 output is equal bit for bit, bfloat16 output equals the
+    rounded numpy values, for other means and deviations too."""
+    from sonicboom_b200.weights import random_init as ri
+    for seed, name, mean, std in [(0, "a", 0.0, 1.0), (2 ** 40 + 5, "model.norm.weight", 1.0, 0.05),
+                                  (11, "lm_head.weight", 0.0, 0.02)]:
+        key = ri.tensor_key(seed, name)
+        want = torch.from_numpy(ri.normal_numpy(n, *key, mean, std))
+        got = ops.random_normal(torch.empty(n, dtype=torch.float32, device=DEV), *key, mean, std).cpu()
+        differs = got.view(torch.int32) != want.view(torch.int32)
+        assert not bool((differs & (want != 0)).any()), int(differs.sum())   # a zero may differ in its sign
+        assert torch.equal(got, want)
+        got16 = ops.random_normal(torch.empty(n, dtype=torch.bfloat16, device=DEV), *key, mean, std).cpu()
+        assert torch.equal(got16, want.to(torch.bfloat16))
+
+
+def test_a_model_made_on_the_device_equals_the_folder_written_without_one(tmp_path):
+    import sonicboom_b200 as sb
+    from conftest import INIT, TINY
+    from sonicboom_b200.models import tensor_requests
+    from sonicboom_b200.config import spec_from_config_dict
+    from sonicboom_b200.weights import RandomSource, SafetensorsDir
+    sb.write_random_model(tmp_path, TINY["C"], seed=17, **INIT["C"])
+    folder = SafetensorsDir(tmp_path)
+    _, spec = spec_from_config_dict(TINY["C"])
+    src = RandomSource(tensor_requests(spec), 17, device=DEV, **INIT["C"])
+    assert sorted(src.names()) == sorted(folder.names())
+    for name in src.names():
+        assert torch.equal(src.tensor(name).cpu(), folder.tensor(name)), name
+    # and the model: the same logits from the folder and from the seed
+    a = sb.Engine(sb.load_model(tmp_path, dtype="float32"), max_tokens=128)
+    b = sb.Engine(sb.random_model(TINY["C"], 17, dtype="float32", **INIT["C"]), max_tokens=128)
+    toks = list(range(3, 60))
+    la = a.step([(a.open(), toks, [len(toks) - 1])])
+    lb = b.step([(b.open(), toks, [len(toks) - 1])])
+    assert torch.equal(la, lb)

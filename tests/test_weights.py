@@ -135,3 +135,51 @@ def test_kept_dtypes():
         def tensor(self, name):
             return torch.ones(2, 2, dtype=torch.float16)
     assert fetch(Src(), "x", bf, "cpu").dtype == bf
+
+
+# ------------------------------------------------------------------ the counter-based generator
+def test_random_tensors_depend_on_seed_name_and_index_only():
+    """Values are a function of (seed, tensor name, element index): the same prefix whatever the
+    length, no dependence on how the work is cut, other values for another seed or name, and a
+    normal distribution."""
+    import numpy as np
+    from sonicboom_b200.weights import random_init as ri
+    k = ri.tensor_key(7, "model.layers.0.mlp.up_proj.weight")
+    a = ri.normal_numpy(10_001, *k)
+    assert a.dtype == np.float32 and a.shape == (10_001,)
+    assert np.array_equal(ri.normal_numpy(37, *k), a[:37])
+    old = ri._CHUNK
+    try:
+        ri._CHUNK = 64                            # chunks of 256 values
+        assert np.array_equal(ri.normal_numpy(10_001, *k), a)
+    finally:
+        ri._CHUNK = old
+    assert not np.array_equal(ri.normal_numpy(64, *ri.tensor_key(8, "model.layers.0.mlp.up_proj.weight")), a[:64])
+    assert not np.array_equal(ri.normal_numpy(64, *ri.tensor_key(7, "model.layers.1.mlp.up_proj.weight")), a[:64])
+    assert ri.tensor_key(7 + 2 ** 32, "x") != ri.tensor_key(7, "x")      # the upper seed bits count
+    z = ri.normal_numpy(400_000, *k).astype(np.float64)
+    assert abs(z.mean()) < 0.01 and abs(z.std() - 1.0) < 0.01
+    assert abs((z ** 3).mean()) < 0.03 and abs((z ** 4).mean() - 3.0) < 0.1
+    assert 4.0 < np.abs(z).max() < 7.0
+    # the words are Philox4x32-10 of {group, 0x5742, 0} under the tensor's key
+    import plain_sampling as ps
+    w = ri._philox(np.asarray([5, 2 ** 33 + 1], dtype=np.uint64), *k)
+    assert [int(x[0]) for x in w] == ps.philox4x32_10((5, 0, 0x5742, 0), k[0] | (k[1] << 32))
+    assert [int(x[1]) for x in w] == ps.philox4x32_10((1, 2, 0x5742, 0), k[0] | (k[1] << 32))
+    shifted = ri.normal_numpy(8, *k, mean=1.0, std=0.05)
+    assert np.array_equal(shifted, np.float32(1.0) + np.float32(0.05) * a[:8])
+
+
+def test_random_source_roles_and_folder(tmp_path):
+    cfg = dict(architectures=["Qwen2ForCausalLM"], hidden_size=32, num_hidden_layers=1,
+               num_attention_heads=2, num_key_value_heads=1, intermediate_size=48, vocab_size=50,
+               max_position_embeddings=64, tie_word_embeddings=True)
+    write_random_model(tmp_path, cfg, seed=3, std=0.5, bias_std=0.25, norm_std=0.125)
+    st = SafetensorsDir(tmp_path)
+    from sonicboom_b200.weights import random_init as ri
+    for name, mean, std in [("model.layers.0.self_attn.q_proj.weight", 0.0, 0.5),
+                            ("model.layers.0.self_attn.k_proj.bias", 0.0, 0.25),
+                            ("model.norm.weight", 1.0, 0.125)]:
+        t = st.tensor(name)
+        want = torch.from_numpy(ri.normal_numpy(t.numel(), *ri.tensor_key(3, name), mean, std))
+        assert torch.equal(t.float().reshape(-1), want.to(torch.bfloat16).float())
