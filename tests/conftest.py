@@ -49,7 +49,9 @@ FP32_TOL = 1e-5      # the float32 path against the plain implementation
 # The bfloat16 path against the plain implementation (for "7B": against the engine's own
 # float32 path), per configuration: about three times the largest error the GPU tests measure
 # (they print what they measured at the end of a run).
-BF16_TOLS = {"A": 2e-2, "B": 2e-2, "C": 2e-2, "D": 2e-2, "7B": 2e-2}
+# Measured on a B200: A 2.0e-3, B 5.5e-3, C 6.2e-3, D 6.5e-3, 7B 1.24e-2 (two layers of 7B sizes:
+# 32 positions x 8,192 logits of a 1,100-token request; kept at the old common bound).
+BF16_TOLS = {"A": 6e-3, "B": 1.6e-2, "C": 1.8e-2, "D": 2e-2, "7B": 2e-2}
 BF16_TOL = 2e-2      # where no configuration is at hand (parts and kernels alone, near ties)
 OBSERVED: dict = {}  # (configuration, dtype) -> largest error seen in this run
 
