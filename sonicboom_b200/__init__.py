@@ -11,7 +11,8 @@ from .engine import Engine, StepEntry, StepError
 from .models import DecoderModel, load_model, random_model
 from .weights import WeightError, write_random_model
 
-__version__ = "0.1.0"
+__version__ = "0.2.0"
+from .buildinfo import build_info, build_info_line
 __all__ = ["ConfigError", "Qwen2Config", "register_architecture", "Engine", "StepEntry",
            "StepError", "DecoderModel", "load_model", "random_model", "WeightError",
-           "write_random_model"]
+           "write_random_model", "build_info", "build_info_line"]

@@ -5,6 +5,7 @@ them (bindings/guile/scheme/sonicboom/inference.scm:586-620).
 
     python -m sonicboom_b200 generate -m DIR --tokens FILE -n 32 [--temperature 0.8 --seed 1 ...]
     python -m sonicboom_b200 random-model --config config.json --seed 7 --out DIR
+    python -m sonicboom_b200 --version
 
 `--tokens FILE` holds token ids separated by white space, one prompt a line; the generated
 ids are printed one line per prompt, space separated.
@@ -44,7 +45,8 @@ def read_prompts(path: str) -> list:
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="sonicboom_b200", description=__doc__,
                                  formatter_class=argparse.RawDescriptionHelpFormatter)
-    sub = ap.add_subparsers(dest="command", required=True)
+    ap.add_argument("--version", action="store_true", help="print the build information and exit")
+    sub = ap.add_subparsers(dest="command")
     g = sub.add_parser("generate", help="continue token-id prompts")
     g.add_argument("-m", "--model", required=True, help="folder with config.json and model.safetensors")
     g.add_argument("--tokens", required=True, help="file of token ids, one prompt a line")
@@ -63,6 +65,12 @@ def main(argv=None) -> int:
     r.add_argument("--bias-std", type=float, default=None)
     r.add_argument("--norm-std", type=float, default=0.0)
     args = ap.parse_args(argv)
+    if args.version:
+        from .buildinfo import build_info_line
+        print(build_info_line())
+        return 0
+    if args.command is None:
+        ap.error("a command is required: generate or random-model")
 
     if args.command == "random-model":
         from .weights import write_random_model

@@ -9,15 +9,12 @@
 #include <stdint.h>
 #include <stdio.h>
 
-enum SbDtype { SB_F32 = 0, SB_BF16 = 1 };
-enum SbStatus { SB_OK = 0, SB_ERR_ARG = 1, SB_ERR_UNSUPPORTED = 2, SB_ERR_CUDA = 3 };
-enum SbEpilogue { SB_EPI_NONE = 0, SB_EPI_BIAS = 1, SB_EPI_RESIDUAL = 2, SB_EPI_SWIGLU = 3 };
+#include "sonicboom_b200.h"      // the public types and every entry point's declaration
 
 // Rows of a fused gate/up matrix alternate in blocks of this many: 8 gate rows, then the 8 up
 // rows of the same outputs.  Every GEMM kernel's SwiGLU epilogue pairs column c with c + 8.
 #define SB_SWIGLU_BLOCK 8
 
-extern "C" const char* sb_last_error();
 void sb_set_error(const char* fmt, ...);
 
 #define SB_FAIL(code, ...)        \
@@ -98,29 +95,6 @@ static inline size_t sb_warm_bytes(const void* ptr, size_t bytes) {
   return (bytes < SB_WARM_MAX ? bytes : SB_WARM_MAX) & ~(size_t)15;
 }
 
-// What may accompany a product (all optional): the RMSNorm of its finished rows, and memory to
-// ask into L2 for a later kernel.
-struct SbLinearExtras {
-  const void* norm_weight;     // null: no norm
-  int norm_weight_dtype;
-  float norm_eps;
-  void* norm_out;
-  int norm_out_dtype;
-  const void* warm;            // null: nothing; else see sb_warm_l2
-  size_t warm_bytes;
-};
-
-// Kernel classes, as bits of the mask that says which kernels get the launch attribute.
-enum SbKernelClass {
-  SB_K_TC5 = 1,          // tcgen05 products
-  SB_K_SKINNY = 2,       // weight-streaming and tiled mma.sync products
-  SB_K_ATTENTION = 4,
-  SB_K_ELEMENTWISE = 8,  // embedding, norms, rotation, casts, small adds
-  SB_K_REDUCE = 16,      // the split-K reduce of the tcgen05 product
-  SB_K_OTHER = 32        // sampler, plain kernels
-};
-
-extern "C" int sb_pdl_enabled();      // per library: the mask of kernel classes; set with sb_set_pdl
 
 template <int CLS = SB_K_OTHER, typename... Exp, typename... Act>
 inline cudaError_t sb_launch(void (*kernel)(Exp...), dim3 grid, dim3 block, size_t smem,

@@ -660,10 +660,6 @@ extern "C" size_t sb_gemm_tc5_scratch_bytes(int M, int N, int K, int n_sms) {
   return (size_t)tiles * splits * swapped_bn(M) * BM * sizeof(float);
 }
 
-extern "C" int sb_rmsnorm(const float* x, const int32_t* rows, int n_rows, int width,
-                          const void* weight, int weight_dtype, float eps, void* out,
-                          int out_dtype, cudaStream_t stream);
-
 // Whether the swapped split-K form can finish these rows with the fused reduce + norm kernel.
 static bool norm_fuses(int M, int N, int K, int n_sms, int epilogue, int out_dtype, int form) {
   const bool normal = form == 1 || (form == 0 && M > 64);

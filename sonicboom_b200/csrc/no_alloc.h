@@ -29,9 +29,7 @@
 //    race on the array and corrupt each other's results: order them.
 #pragma once
 
-#include <cuda_runtime.h>
-#include <stddef.h>
-#include <stdint.h>
+#include "sonicboom_b200.h"     /* sb_stream_t (the runtime's cudaStream_t) and the ordinary entry points */
 
 #define SB_STATIC_SCRATCH_BYTES (8u << 20)
 
@@ -39,12 +37,15 @@
 extern "C" {
 #endif
 
-// Same arguments and results as sb_attention, without the scratch pointer and size.
+// The arguments of sb_attention that describe the step, with the same meanings and results;
+// what sb_attention takes besides them is not needed here: no scratch pointer and size, no
+// merge counters and their count (both are inside the library), no n_pages and n_sms (this
+// entry point runs decode steps only), no L2 hint.
 int sb_attention_decode_static(const void* q, void* out, int n_rows, int n_seqs, int max_new,
                                const int32_t* seq_row0, const int32_t* seq_pos0,
                                const int32_t* page_off, const int32_t* page_ids, int page_size,
                                const void* cache, int n_q_heads, int n_kv_heads, int hd,
-                               int window, float scale, int max_len, cudaStream_t stream);
+                               int window, float scale, int max_len, sb_stream_t stream);
 
 // Bytes of the built-in scratch array (SB_STATIC_SCRATCH_BYTES).
 size_t sb_attention_static_scratch_bytes(void);

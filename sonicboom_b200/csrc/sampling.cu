@@ -17,14 +17,6 @@
 
 #include "common.cuh"
 
-struct SbSampleParams {
-  float temperature, top_p, min_p, repeat_penalty, presence_penalty, frequency_penalty;
-  uint32_t top_k;
-  int32_t history_len;       // tokens of this row in `history` (already cut to repeat_last_n)
-  uint64_t seed;
-  uint64_t position;
-};
-
 namespace {
 
 constexpr int THREADS = 1024;

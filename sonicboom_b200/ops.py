@@ -11,6 +11,7 @@ import ctypes
 
 import torch
 
+from . import abi as _abi
 from .csrc import build as _build
 
 F32, BF16 = 0, 1
@@ -29,9 +30,7 @@ _lib = None
 def lib() -> ctypes.CDLL:
     global _lib
     if _lib is None:
-        l = _build.load()
-        l.sb_last_error.restype = ctypes.c_char_p
-        _lib = l
+        _lib = _abi.apply(_build.load(), _abi.CORE)
     return _lib
 
 
@@ -288,7 +287,6 @@ def _tc5_workspace(M: int, N: int, K: int, device):
     """Workspace of the split-K decode product: the partial tiles.  One buffer per device
     serves every call on the stream; it only grows."""
     l = lib()
-    l.sb_gemm_tc5_scratch_bytes.restype = ctypes.c_size_t
     need = int(l.sb_gemm_tc5_scratch_bytes(M, N, K, _sm_count(device)))
     if need == 0:
         return None
@@ -357,10 +355,7 @@ def attention_lib(head_dim: int):
     outside what those kernels are written for (multiples of 16 up to 256)."""
     if head_dim not in _attn_libs:
         if head_dim in _build.HEAD_DIMS:
-            l = _build.load_attention(head_dim)
-            l.sb_last_error.restype = ctypes.c_char_p
-            l.sb_attention_scratch_bytes.restype = ctypes.c_size_t
-            _attn_libs[head_dim] = l
+            _attn_libs[head_dim] = _abi.apply(_build.load_attention(head_dim), _abi.ATTENTION)
         else:
             _attn_libs[head_dim] = None
     return _attn_libs[head_dim]

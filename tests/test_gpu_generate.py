@@ -92,6 +92,21 @@ def test_dependent_launch_changes_no_token(model_dirs):
     assert ops.tc5_status() == 0 and ops.attention_status(TINY["B"]["head_dim"]) == 0
 
 
+def test_trace_ranges_change_no_token(model_dirs):
+    """With the opt-in NVTX ranges on (per step, per schedule entry, per captured decode step)
+    the same tokens come out."""
+    from sonicboom_b200 import ops
+    model = llm.model_load(model_dirs["B"], dtype="bfloat16")
+    prompts = prompts_for("B", [3, 40, 90], seed=15)
+    off = llm.generate_batch(model, prompts, max_tokens=12, ignore_eos=True)
+    ops.set_trace(True)
+    try:
+        on = llm.generate_batch(model, prompts, max_tokens=12, ignore_eos=True)
+    finally:
+        ops.set_trace(False)
+    assert on == off
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_stop_tokens_and_eos(model_dirs, oracles, dtype):
     model = llm.model_load(model_dirs["A"], dtype=dtype)
