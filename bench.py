@@ -142,11 +142,19 @@ def decode_flops_per_token(cfg) -> float:
     return per_layer * cfg["num_hidden_layers"]
 
 
+QWEN25_1P5B = dict(QWEN25_7B, hidden_size=1536, num_attention_heads=12, num_key_value_heads=2,
+                   intermediate_size=8960, vocab_size=151936, tie_word_embeddings=True)
+QWEN25_32B = dict(QWEN25_7B, hidden_size=5120, num_hidden_layers=64, num_attention_heads=40,
+                  num_key_value_heads=8, intermediate_size=27648)
+REPETITIONS = 3       # timed regions of K steps each; the median is reported
+
+
 def run(args) -> int:
     import torch
     import sonicboom_b200 as sb
     from sonicboom_b200.engine.decode import DecodeLoop
     from sonicboom_b200 import llm, ops
+    from sonicboom_b200.sampling import Sampling
 
     torch.cuda.set_device(0)
     dev = "cuda:0"
@@ -159,56 +167,72 @@ def run(args) -> int:
     model = sb.random_model(cfg, seed=0, dtype="bfloat16", device=dev, std=0.02)
     torch.cuda.synchronize()
     load_s = time.time() - t0
-    wbytes = weight_bytes(model)
-    kv_bytes_per_token = sum(g.bytes_per_token() for g in
-                             sb.Engine(model, max_tokens=64).cache.groups)
     gen = torch.Generator().manual_seed(1)
 
-    def prompts(n):
-        return [torch.randint(0, cfg["vocab_size"], (PROMPT_LEN,), generator=gen).tolist()
+    def kv_bytes_per_token(m):
+        return sum(g.bytes_per_token() for g in sb.Engine(m, max_tokens=64).cache.groups)
+
+    def prompts(n, length=PROMPT_LEN, vocab=None):
+        return [torch.randint(0, vocab or cfg["vocab_size"], (length,), generator=gen).tolist()
                 for _ in range(n)]
 
-    def decode_point(batch, steps, warmup, clocks=None, graph=True):
-        """Prefills `batch` prompts (8 at a time), then times `steps` steps of the decode loop
-        on the device with CUDA events."""
-        engine = sb.Engine(model, max_tokens=batch * CONTEXT, n_slots=batch)
+    def decode_point(m, batch, steps, warmup, clocks=None, graph=True, prompt_len=PROMPT_LEN,
+                     context=CONTEXT, real_prompt=None, reps=REPETITIONS):
+        """Prefills `batch` prompts (8 at a time), then times regions of `steps` steps of the
+        decode loop on the device with CUDA events: after `warmup` steps and one untimed region,
+        `reps` regions back to back; the median region is the result.
+        The sequences decode from prompt_len to context positions; the timed steps are the ones
+        around the middle of that stretch.  Instead of decoding every token up to there, the
+        sequences' lengths are moved forward (the skipped positions hold zeros in the cache; a
+        step reads the same bytes either way).  `real_prompt` < prompt_len prefills only that
+        many tokens of each prompt and moves the lengths forward over the rest as well."""
+        real = real_prompt or prompt_len
+        engine = sb.Engine(m, max_tokens=batch * context, n_slots=batch)
         slots = [engine.open() for _ in range(batch)]
-        ps = prompts(batch)
+        ps = prompts(batch, real, m.spec.vocab)
         first = []
         for i in range(0, batch, 8):
             lg = engine.step([(s, p, [len(p) - 1]) for s, p in zip(slots[i:i + 8], ps[i:i + 8])])
             first += lg.argmax(dim=-1).tolist()
-        # The sequences decode from 2,048 to 4,096 positions; the timed steps are the ones
-        # around the middle of that stretch.  Instead of decoding every token up to there, the
-        # sequences' lengths are moved forward (the skipped positions hold zeros in the cache;
-        # a step reads the same bytes either way).
-        skip = max(0, (CONTEXT + PROMPT_LEN) // 2 - (warmup + steps) // 2 - PROMPT_LEN)
-        skip = min(skip, CONTEXT - PROMPT_LEN - (warmup + steps + 2))
+        room = context - prompt_len
+        reps = max(1, min(reps, (room - warmup - 2) // steps - 1))
+        total = warmup + (reps + 1) * steps
+        skip = max(0, min((context + prompt_len) // 2 - total // 2 - real, context - real - total - 2))
         for s in slots:
-            engine.cache.reserve(s, PROMPT_LEN + skip)
-            engine.cache.advance(s, PROMPT_LEN + skip)
-        loop = DecodeLoop(engine, slots, warmup + steps + 2, use_graph=graph)
-        loop.run_device(first, warmup)
+            engine.cache.reserve(s, real + skip)
+            engine.cache.advance(s, real + skip)
+        loop = DecodeLoop(engine, slots, total + 2, use_graph=graph)
+        loop.run_device(first, warmup + steps)               # warm-up, and one untimed region
         torch.cuda.synchronize()
-        ctx_start = engine.length(slots[0]) + warmup
-        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ctx_start = engine.length(slots[0]) + warmup + steps
         if clocks is not None:
             clocks.__enter__()
-        start.record()
-        loop.run_device(None, steps)
-        end.record()
-        torch.cuda.synchronize()
+        times = []
+        for _ in range(reps):
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            loop.run_device(None, steps)
+            end.record()
+            torch.cuda.synchronize()
+            times.append(start.elapsed_time(end))
         if clocks is not None:
             clocks.__exit__()
-        ms = start.elapsed_time(end)
+        mid = sorted(range(reps), key=lambda i: times[i])[reps // 2]      # the median region
+        ms = times[mid]
         launches = loop.launches_per_step * steps
         loop.close()
         for s in slots:
             engine.close(s)
         del engine, loop
         torch.cuda.empty_cache()
+        nbytes = weight_bytes(m) + batch * (ctx_start + mid * steps + steps / 2.0) * kv_bytes_per_token(m)
         return {"tok_s": batch * steps / (ms / 1e3), "ms_per_step": ms / steps, "launches": launches,
-                "bytes_per_step": wbytes + batch * (ctx_start + steps / 2.0) * kv_bytes_per_token}
+                "bytes_per_step": nbytes, "frac": nbytes / (ms / steps / 1e3) / 1e9 / pk["hbm_gbs"],
+                "repetitions": reps, "all_ms_per_step": [t / steps for t in times]}
+
+    def point_record(r):
+        return {"tok_s": round(r["tok_s"], 1), "ms_per_step": round(r["ms_per_step"], 4),
+                "bytes_per_step": int(r["bytes_per_step"]), "frac": round(r["frac"], 4)}
 
     def e2e_point(batch, steps, warmup):
         """The same through the Python entry point: host token ids in, host token ids out.
@@ -232,44 +256,109 @@ def run(args) -> int:
         torch.cuda.empty_cache()
         return {"tok_s": batch * steps / dt, "h2d": 4 * batch, "d2h": 4 * batch}
 
+    def session_point(steps, warmup):
+        """Batch 1 through llm.Session (`boom_llm_prefill` / `boom_llm_decode`): wall time
+        per token of one decode call, after `warmup` tokens."""
+        sess = llm.session_new(llm.Model(model), CONTEXT)
+        sess.prefill(prompts(1)[0])
+        stamps = []
+        sess.decode(Sampling(max_tokens=warmup + steps + 1), cb=lambda t: stamps.append(time.perf_counter()) or 0)
+        sess.free()
+        dt = stamps[warmup + steps] - stamps[warmup]
+        del sess
+        torch.cuda.empty_cache()
+        return {"tok_s": round(steps / dt, 1), "ms_per_step": round(dt / steps * 1e3, 4),
+                "positions": f"{PROMPT_LEN}..{PROMPT_LEN + warmup + steps}"}
+
     if args.only == "decode":
         # a small case for profilers: the decode point alone (with --eager: kernel by kernel)
-        r = decode_point(args.batch, args.steps, args.warmup, graph=not args.eager)
+        r = decode_point(model, args.batch, args.steps, args.warmup, graph=not args.eager, reps=1)
         print(json.dumps({"only": "decode", "layers": cfg["num_hidden_layers"], "batch": args.batch,
                           "ms_per_step": round(r["ms_per_step"], 4), "tok_s": round(r["tok_s"], 1)}))
         return 0
 
+    def prefill_point(m, n_tokens, reps):
+        engine = sb.Engine(m, max_tokens=n_tokens, n_slots=1)
+        (p,) = prompts(1, n_tokens, m.spec.vocab)
+        times = []
+        for i in range(1 + reps):
+            s = engine.open()
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            engine.step([(s, p, [n_tokens - 1])])
+            end.record()
+            torch.cuda.synchronize()
+            engine.close(s)
+            if i > 0:
+                times.append(start.elapsed_time(end))
+        del engine
+        torch.cuda.empty_cache()
+        return sorted(times)[len(times) // 2]
+
+    def prefill_flops(c, n_tokens):
+        hd_ = c["hidden_size"] // c["num_attention_heads"]
+        return n_tokens * decode_flops_per_token(c) + \
+            c["num_hidden_layers"] * 4 * c["num_attention_heads"] * hd_ * n_tokens * n_tokens / 2 + \
+            2 * c["hidden_size"] * c["vocab_size"]
+
     # prefill of one 2,048-token prompt
-    engine = sb.Engine(model, max_tokens=PROMPT_LEN, n_slots=1)
-    (p,) = prompts(1)
-    times = []
-    for i in range(1 + args.prefill_reps):
-        s = engine.open()
-        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        start.record()
-        engine.step([(s, p, [PROMPT_LEN - 1])])
-        end.record()
-        torch.cuda.synchronize()
-        engine.close(s)
-        if i > 0:
-            times.append(start.elapsed_time(end))
-    prefill_ms = sorted(times)[len(times) // 2]
+    prefill_ms = prefill_point(model, PROMPT_LEN, args.prefill_reps)
     hd = cfg["hidden_size"] // cfg["num_attention_heads"]
-    prefill_flops = PROMPT_LEN * decode_flops_per_token(cfg) + \
-        cfg["num_hidden_layers"] * 4 * cfg["num_attention_heads"] * hd * PROMPT_LEN * PROMPT_LEN / 2 + \
-        2 * cfg["hidden_size"] * cfg["vocab_size"]
-    del engine
     if args.only == "prefill":
         print(json.dumps({"only": "prefill", "layers": cfg["num_hidden_layers"], "tokens": PROMPT_LEN,
                           "ms": round(prefill_ms, 3)}))
         return 0
 
     clocks = ClockSampler()
-    main = decode_point(args.batch, args.steps, args.warmup, clocks=clocks)
+    main = decode_point(model, args.batch, args.steps, args.warmup, clocks=clocks)
     e2e = e2e_point(args.batch, args.steps, args.warmup)
     points = {}
     for b in (1, 64):
-        points[f"decode_b{b}"] = round(decode_point(b, args.steps, args.warmup)["tok_s"], 1)
+        points[f"decode_b{b}"] = point_record(decode_point(model, b, args.steps, args.warmup))
+    if not args.no_extras:
+        points["session_decode_b1"] = session_point(min(args.steps, 128), 8)
+    ops.check_status()
+
+    if not args.no_extras:
+        # Further sizes of the same architecture; they do not enter `value`.
+        del model
+        torch.cuda.empty_cache()
+        # Qwen2.5-1.5B sizes: 64 prompts of 16..1,024 tokens, 256 new tokens each at temperature
+        # 0.7, through generate_batch (prefill, sampling and the host loop included)
+        m15 = sb.random_model(QWEN25_1P5B, seed=0, dtype="bfloat16", device=dev, std=0.02)
+        lens = torch.randint(16, 1025, (64,), generator=gen).tolist()
+        ps = [torch.randint(0, QWEN25_1P5B["vocab_size"], (n,), generator=gen).tolist() for n in lens]
+        llm.generate_batch(llm.Model(m15), ps[:4], max_tokens=8, ignore_eos=True, temperature=0.7, seed=1)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        outs = llm.generate_batch(llm.Model(m15), ps, max_tokens=256, ignore_eos=True,
+                                  temperature=0.7, seed=1)
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        points["qwen2.5-1.5b_generate_64x256_t0.7"] = {
+            "tok_s": round(sum(len(o) for o in outs) / dt, 1), "seconds": round(dt, 3),
+            "prompt_tokens": sum(lens), "new_tokens": sum(len(o) for o in outs), "layers": 28}
+        del m15
+        torch.cuda.empty_cache()
+        # Qwen2.5-32B sizes: prefill of 8,192 tokens; decode at batch 1 and 16 around position
+        # 12,288 of 8,192..16,384 (64 tokens of each prompt are prefilled, the lengths are moved
+        # forward over the rest: the cache holds zeros there and a step reads the same bytes)
+        c32 = dict(QWEN25_32B)
+        if args.layers_32b:
+            c32["num_hidden_layers"] = args.layers_32b
+        m32 = sb.random_model(c32, seed=0, dtype="bfloat16", device=dev, std=0.02)
+        ms32 = prefill_point(m32, 8192, 1)
+        rec = {"layers": c32["num_hidden_layers"], "layers_full_model": 64,
+               "prefill_8192": {"tok_s": round(8192 / (ms32 / 1e3), 1), "ms": round(ms32, 2),
+                                "frac": round(prefill_flops(c32, 8192) / (ms32 / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}}
+        for b in (1, 16):
+            rec[f"decode_b{b}"] = point_record(decode_point(m32, b, 16, 4, prompt_len=8192, context=16384,
+                                                            real_prompt=64))
+        points["qwen2.5-32b"] = rec
+        del m32
+        torch.cuda.empty_cache()
+        ops.check_status()
+
     achieved = main["bytes_per_step"] / (main["ms_per_step"] / 1e3) / 1e9
     out = {
         "metric": "decode tok/s at batch 8 (Qwen2.5-7B sizes, 2,048-token prompts, context 4,096)",
@@ -285,18 +374,21 @@ def run(args) -> int:
                    "prompt_len": PROMPT_LEN, "parallelism": "none (1 GPU)",
                    "decode_positions": "timed steps centred on position 3072 of 2048..4096",
                    "l2": "inputs larger than L2 (weights read once per step)",
-                   "peaks": pk["source"]},
+                   "peaks": pk["source"],
+                   "repetitions": f"median of {main['repetitions']} timed regions of {args.steps} steps "
+                                  f"after {args.warmup} + {args.steps} untimed steps"},
         "e2e": {"value": round(e2e["tok_s"], 1), "unit": "tok/s",
                 "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"]},
         "gpu_launches": int(main["launches"]),
         "clocks": clocks.summary(),
         "prefill": {"value": round(PROMPT_LEN / (prefill_ms / 1e3), 1), "tokens": PROMPT_LEN,
                     "ms": round(prefill_ms, 3),
-                    "frac": round(prefill_flops / (prefill_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)},
+                    "frac": round(prefill_flops(cfg, PROMPT_LEN) / (prefill_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"],
                      "unit": "GB/s", "frac": round(achieved / pk["hbm_gbs"], 4)},
         "points": points,
         "load_s": round(load_s, 1),
+        "build": sb.build_info_line(),
     }
     print(json.dumps(out))
     return 0
@@ -312,6 +404,11 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=0,
                     help="run fewer layers than the model has (both numbers go into config)")
     ap.add_argument("--prefill-reps", type=int, default=3)
+    ap.add_argument("--no-extras", action="store_true",
+                    help="leave out the points beyond the headline configuration (the session "
+                         "entry point, the 1.5B and 32B sizes)")
+    ap.add_argument("--layers-32b", type=int, default=0,
+                    help="run the 32B sizes with fewer than their 64 layers (both numbers are recorded)")
     ap.add_argument("--only", choices=["decode", "prefill"], default=None,
                     help="run one phase only and print a short line (small cases for profilers)")
     ap.add_argument("--eager", action="store_true",

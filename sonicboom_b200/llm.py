@@ -66,6 +66,26 @@ class Session:
         self.tokens: list = []          # prompt + everything decoded so far
         self._logits = None             # logits at the last position, for the next token
         self._pending = None            # a produced token that was not fed to the model yet
+        self._loop = None               # the captured decode step while one is open
+        self._loop_key = None           # the sampling fields that loop was captured with
+
+    def _close_loop(self) -> None:
+        loop, self._loop, self._loop_key = self._loop, None, None
+        if loop is not None:
+            loop.close()
+
+    def _loop_for(self, s: Sampling):
+        """The captured decode step for this sampling record (made at the first token that
+        needs it and kept until the prompt, the record or the context's end changes that), or
+        None when the engine cannot capture it (penalties read the token history on the host)."""
+        key = (s.temperature, s.top_p, s.top_k, s.seed, s.min_p)
+        if self._loop is not None and self._loop_key != key:
+            self._close_loop()
+        if self._loop is None:
+            room = self.n_ctx - self.engine.length(self.slot)
+            self._loop = self.engine.decode_loop([self.slot], [room], [s])
+            self._loop_key = key if self._loop is not None else None
+        return self._loop
 
     def prefill(self, tokens) -> int:
         """`boom_llm_prefill`: sets the prompt.  Returns how many leading tokens were reused
@@ -75,6 +95,7 @@ class Session:
             raise ValueError("prefill needs a non-empty prompt")
         if len(tokens) > self.n_ctx:
             raise ValueError(f"prompt of {len(tokens)} tokens exceeds n_ctx = {self.n_ctx}")
+        self._close_loop()
         reused = 0
         if self.slot is not None:
             common = 0
@@ -98,27 +119,37 @@ class Session:
 
     def decode(self, sampling: Sampling, cb: Optional[Callable] = None) -> list:
         """`boom_llm_decode`: up to sampling.max_tokens tokens; `cb(token)` is called for each
-        in order and a non-zero return stops the decode.  Returns the tokens produced."""
+        in order and a non-zero return stops the decode.  Returns the tokens produced.  The
+        first token after a prefill comes from the prefill's logits; every later one from the
+        captured decode step (one graph launch per token, the token id in and out through pinned
+        host memory), as the reference replays its captured step per token
+        (core/src/model/gemma4_plan.cpp:1650-1696)."""
         if self.slot is None or (self._logits is None and self._pending is None):
             raise RuntimeError("decode requires a prompt: call prefill first")
         s = sampling.checked()
         out = []
         while len(out) < s.max_tokens:
-            if self._logits is None:             # feed the token the last call ended with
-                if len(self.tokens) > self.n_ctx:
-                    raise RuntimeError(f"the session's context of {self.n_ctx} tokens is full")
-                self._logits = self.engine.step([(self.slot, [self._pending], [0])])
             if len(self.tokens) >= self.n_ctx:
                 raise RuntimeError(f"the session's context of {self.n_ctx} tokens is full")
-            (tok,) = self.sampler.sample(self._logits, [s], [len(self.tokens)], [self.tokens])
+            if self._logits is not None:
+                (tok,) = self.sampler.sample(self._logits, [s], [len(self.tokens)], [self.tokens])
+                self._logits = None
+            else:                                # feed the last token, get the next
+                loop = self._loop_for(s)
+                if loop is not None:
+                    (tok,) = loop.step_host([self._pending])
+                else:
+                    logits = self.engine.step([(self.slot, [self._pending], [0])])
+                    (tok,) = self.sampler.sample(logits, [s], [len(self.tokens)], [self.tokens])
             out.append(tok)
             self.tokens.append(tok)
-            self._pending, self._logits = tok, None
+            self._pending = tok
             if cb is not None and cb(tok):
                 break
         return out
 
     def free(self) -> None:
+        self._close_loop()
         if self.slot is not None:
             self.engine.close(self.slot)
             self.slot = None
