@@ -21,6 +21,7 @@
 // Every wait on an mbarrier is bounded; when a bound is hit the kernel records a code in a
 // status word, stops issuing work and leaves normally (sb_tc5_status reads the word).
 #include <cooperative_groups.h>
+#include <stdlib.h>
 
 #include "tc5.cuh"
 
@@ -68,17 +69,18 @@ constexpr int smem_bytes(int bn, int stages) { return stages * stage_bytes(bn) +
 // Epilogue of one 32-row x 32-column chunk of the normal form.  The accumulator chunk (a thread
 // holds one row) is passed through a 32 x 33 shared-memory tile of the warp and written out row
 // by row with a lane per column, so that global accesses coalesce.
-template <typename TO>
+// NC = 32, or 16 for the last chunk of a tile whose width is an odd multiple of 16.
+template <typename TO, int NC = 32>
 __device__ __forceinline__ void store_chunk(const Tc5Params& p, float* stage, const uint32_t (&r)[32],
                                             int m_base, int n0, int lane) {
   __syncwarp();
 #pragma unroll
-  for (int j = 0; j < 32; ++j) stage[lane * 33 + j] = __uint_as_float(r[j]);
+  for (int j = 0; j < NC; ++j) stage[lane * 33 + j] = __uint_as_float(r[j]);
   __syncwarp();
   if (p.epilogue == SB_EPI_SWIGLU) {
-    // 16 outputs per row: lanes 0-15 take an even row, lanes 16-31 the next one
+    // 16 outputs per row (8 of a 16-column chunk): lanes 0-15 take an even row, lanes 16-31 the next one
     const int o = lane & 15, src = (o >> 3) * 16 + (o & 7);
-    const bool live = n0 / 2 + o < p.N / 2;
+    const bool live = n0 / 2 + o < p.N / 2 && o < NC / 2;
 #pragma unroll 4
     for (int rr = 0; rr < 32; rr += 2) {
       const int row = rr + (lane >> 4), m = m_base + row;
@@ -89,7 +91,7 @@ __device__ __forceinline__ void store_chunk(const Tc5Params& p, float* stage, co
     return;
   }
   const int n = n0 + lane;
-  const bool live = n < p.N;
+  const bool live = n < p.N && lane < NC;
   float add = 0.0f;
   if (p.epilogue == SB_EPI_BIAS && live)
     add = p.bias_dtype == SB_F32 ? bias_at<float>(p.bias, n) : bias_at<bf16>(p.bias, n);
@@ -406,6 +408,12 @@ gemm_tc5_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
         const int n0 = tile_b * BN + c * 32;
         if (n0 < p.N) store_chunk<TO>(p, stage, r, m_base, n0, lane);
       }
+      if (BN % 32) {                                   // a last chunk of 16 columns
+        uint32_t r[32];
+        tmem_ld16(t_row + (BN / 32) * 32, r);
+        const int n0 = tile_b * BN + (BN / 32) * 32;
+        if (n0 < p.N) store_chunk<TO, 16>(p, stage, r, m_base, n0, lane);
+      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(acc_empty0 + 8 * acc);
@@ -613,12 +621,25 @@ int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, const Tc5Par
   return SB_OK;
 }
 
-// Tile width of the persistent kernel: the candidate that needs the least (waves x width).
+// Tile width of the persistent kernel.  A product takes about (waves of tiles over the SMs) x
+// (tile width) units of time, so the candidate with the smallest product wins, the wider one
+// on a tie (fewer tiles, fewer epilogues).  Any multiple of 16 up to 256 is a legal MMA width
+// at 128 rows; the candidates are the ones that fit a four-stage ring.  For 2,048 rows and
+// 3,584 features on 148 SMs: 256 wide gives 224 tiles (2 waves, the second half empty: 512
+// units), 224 wide 256 tiles (448), 208 wide 288 tiles (1.95 waves: 416).
+constexpr int PERSIST_BNS[] = {256, 240, 224, 208, 192};
 int persistent_bn(int M, int N, int n_sms) {
+  static const int forced = [] {                  // SB_TC5_BN=<width>: one width for every product (for measurements)
+    const char* e = getenv("SB_TC5_BN");
+    const int v = e ? atoi(e) : 0;
+    for (int bn : PERSIST_BNS) if (bn == v) return v;
+    return 0;
+  }();
+  if (forced) return forced;
   const int tiles_m = (M + BM - 1) / BM;
   int best = 0;
   long best_cost = 0;
-  for (int bn : {256, 224}) {
+  for (int bn : PERSIST_BNS) {
     const long tiles = (long)tiles_m * ((N + bn - 1) / bn);
     const long cost = ((tiles + n_sms - 1) / n_sms) * bn;
     if (!best || cost < best_cost) { best = bn; best_cost = cost; }
@@ -716,7 +737,7 @@ static int tc5_run(const void* A, int a_dtype, const void* W, int w_dtype, int M
   // form: 0 picks by the number of rows, 1 forces the normal form, 2 the swapped form
   const bool normal = form == 1 || (form == 0 && M > 64);
   if (form == 2 && M > 64) SB_FAIL(SB_ERR_UNSUPPORTED, "sb_gemm_tc5: the swapped form takes at most 64 rows");
-  if (normal && N >= 224 && n_sms > 0) {
+  if (normal && N >= 192 && n_sms > 0) {
     // many rows, wide output: the persistent kernel
     const int bn = persistent_bn(M, N, n_sms);
     p.tiles_a = (M + BM - 1) / BM;
@@ -726,12 +747,13 @@ static int tc5_run(const void* A, int a_dtype, const void* W, int w_dtype, int M
     const long n_tiles = (long)p.tiles_a * p.tiles_b;
     if (n_tiles > 2147483647L) SB_FAIL(SB_ERR_UNSUPPORTED, "sb_gemm_tc5: too many tiles");
     const int blocks = (int)(n_tiles < n_sms ? n_tiles : n_sms);
-    if (bn == 256) {
-      if (out_dtype == SB_F32) return launch_persistent<256, 4, float>(ma, mb, p, blocks, stream);
-      return launch_persistent<256, 4, bf16>(ma, mb, p, blocks, stream);
-    }
-    if (out_dtype == SB_F32) return launch_persistent<224, 4, float>(ma, mb, p, blocks, stream);
-    return launch_persistent<224, 4, bf16>(ma, mb, p, blocks, stream);
+#define SB_TC5_PERSIST(BN_)                                                                        \
+    if (bn == BN_)                                                                                 \
+      return out_dtype == SB_F32 ? launch_persistent<BN_, 4, float>(ma, mb, p, blocks, stream)     \
+                                 : launch_persistent<BN_, 4, bf16>(ma, mb, p, blocks, stream);
+    SB_TC5_PERSIST(256) SB_TC5_PERSIST(240) SB_TC5_PERSIST(224) SB_TC5_PERSIST(208) SB_TC5_PERSIST(192)
+#undef SB_TC5_PERSIST
+    SB_FAIL(SB_ERR_UNSUPPORTED, "sb_gemm_tc5: no persistent kernel of width %d", bn);
   }
   if (normal) {
     constexpr int BN = 128;

@@ -123,6 +123,25 @@ def test_linear_epilogues(M, N, K, dtype, kernel):
     assert ops.tc5_status() == 0
 
 
+@pytest.mark.parametrize("M,N,K", [(1280, 3568, 72), (1280, 3344, 72), (1280, 3120, 72), (2048, 3568, 136),
+                                   (200, 528, 328)])
+def test_persistent_product_at_every_tile_width(M, N, K):
+    """Sizes for which the persistent tcgen05 product picks each of its tile widths on 148 SMs
+    (256, 240, 224, 208, 192), with a last tile that is only partly inside the matrix: every
+    epilogue against the float64 product.  Widths that are odd multiples of 16 end in a chunk
+    of 16 columns."""
+    dt = torch.bfloat16
+    a, w = rnd(M, K, dtype=dt), rnd(N, K, dtype=dt, scale=K ** -0.5, seed=1)
+    bias, res = rnd(N, dtype=dt, seed=2), rnd(M, N, seed=3)
+    for epi, odt in [(ops.EPI_NONE, torch.float32), (ops.EPI_BIAS, dt), (ops.EPI_RESIDUAL, torch.float32),
+                     (ops.EPI_SWIGLU, dt)]:
+        out = torch.empty(M, N // 2 if epi == ops.EPI_SWIGLU else N, dtype=odt, device=DEV)
+        ops.linear(a, w, out, epi, bias=bias if epi == ops.EPI_BIAS else None,
+                   residual=res.clone() if epi == ops.EPI_RESIDUAL else None, kernel="tc5")
+        close(out, linear_ref(a, w, epi, bias, res), 1e-5 if odt == torch.float32 else 5e-3)
+    assert ops.tc5_status() == 0
+
+
 @pytest.mark.parametrize("kernel", ["plain", "skinny", "tiled", "tc5"])
 def test_linear_rows_do_not_depend_on_the_batch(kernel):
     a, w = rnd(40, 256, dtype=torch.bfloat16), rnd(88, 256, dtype=torch.bfloat16, seed=1)
