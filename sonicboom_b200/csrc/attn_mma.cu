@@ -166,10 +166,13 @@ __device__ __forceinline__ void tile_step(const uint32_t (&qf)[HD / 16][4], uint
     m[r] = m_new;
     l[r] *= alpha[r];
   }
+  // most tiles leave every row's maximum where it was: the factors are exactly 1 then
+  if (__any_sync(0xffffffffu, alpha[0] != 1.0f || alpha[1] != 1.0f)) {
 #pragma unroll
-  for (int j = 0; j < HD / 8; ++j) {
-    o[j][0] *= alpha[0]; o[j][1] *= alpha[0];
-    o[j][2] *= alpha[1]; o[j][3] *= alpha[1];
+    for (int j = 0; j < HD / 8; ++j) {
+      o[j][0] *= alpha[0]; o[j][1] *= alpha[0];
+      o[j][2] *= alpha[1]; o[j][3] *= alpha[1];
+    }
   }
 #pragma unroll
   for (int j = 0; j < NKEYS / 8; ++j) {
