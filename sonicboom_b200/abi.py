@@ -48,6 +48,7 @@ ATTENTION = {
     "sb_attention_head_dim": ("i", ""),
     "sb_attention_force_mma": ("v", "i"),
     "sb_attention_status": ("i", ""),
+    "sb_attention_last_launches": ("i", ""),
     "sb_attention_scratch_bytes": ("z", "iiiii"),
     "sb_attention": ("i", "ppiiippppipiiiifpzpiiiipzs"),
     "sb_attention_decode_static": ("i", "ppiiippppipiiiifis"),

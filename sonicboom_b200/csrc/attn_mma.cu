@@ -588,10 +588,19 @@ int n_splits_for(int max_len) {
 
 }  // namespace
 
+#ifdef SB_ATTN_TC5
+#include "attn_decode_tma.cuh"
+#endif
+
 extern "C" int sb_attention_head_dim() { return HD; }
 
-// Prefill kernel choice: 0 (default) the tensor-memory kernel where it applies, 1 always the
-// mma.sync kernel (tests compare the two).
+// Kernels the last sb_attention call of this library launched (1, or 2 when a split merge followed).
+static int g_last_launches = 1;
+extern "C" int sb_attention_last_launches() { return g_last_launches; }
+
+// Kernel choice: 0 (default) the tensor-memory prefill kernel where it applies and the persistent
+// TMA decode kernel where it applies and pays, 1 always the earlier mma.sync kernels, 2 the
+// persistent decode kernel whatever the number of splits (tests compare them).
 static int g_force_mma = 0;
 extern "C" void sb_attention_force_mma(int on) { g_force_mma = on; }
 
@@ -671,6 +680,60 @@ extern "C" int sb_attention(const void* q, void* out, int n_rows, int n_seqs, in
     // The L2 hint pays only when many SMs share it: a block's share goes through its SM's copy
     // engine, and a few blocks with megabytes each hold the kernel up (a step of one 768-key
     // sequence, 16 blocks: 2.5 us a layer slower than without the hint).
+    g_last_launches = 1;
+#ifdef SB_ATTN_TC5
+    // Head sizes 64 and 128, many splits: persistent blocks that stream the pages with TMA, then
+    // the merge of the splits as a kernel of its own.
+    const long cache_rows_d = (long)n_pages * 2 * n_kv_heads * KT;
+    const long n_items = (long)n_seqs * n_kv_heads * p.n_splits;
+    // It pays from about one wave of the earlier kernel's blocks on (three per SM): measured on
+    // B200 at 28/4 heads of 128 and 3,072 keys, 8 sequences (416 splits) take 15.1 us there and
+    // 17.0 us here, 12 sequences 25.2 and 23.5 us, 64 sequences 87.6 and 77.0 us.
+    static bool dt_misaligned = false;
+    if (g_force_mma != 1 && !dt_misaligned && n_pages > 0 && n_sms > 0 && cache_rows_d < 2147483647L &&
+        n_items < 2147483647L && (n_items > 3L * n_sms || g_force_mma == 2) && (size_t)2 * DEC_ROWS * p.n_splits * sizeof(float) <= 48 * 1024) {
+      static bool configured_dt = false;
+      if (!configured_dt) {
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_tma_kernel,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, DT_SMEM);
+        if (e == cudaSuccess)                          // all of the SM's memory as shared memory: three blocks fit
+          e = cudaFuncSetAttribute(attn_decode_tma_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                   cudaSharedmemCarveoutMaxShared);
+        if (e != cudaSuccess)
+          SB_FAIL(SB_ERR_CUDA, "sb_attention: shared memory opt-in failed: %s", cudaGetErrorString(e));
+        configured_dt = true;
+      }
+      CUtensorMap map_kv;
+      if (!t5_make_map(&map_kv, cache, cache_rows_d))
+        SB_FAIL(SB_ERR_CUDA, "sb_attention: cuTensorMapEncodeTiled failed");
+      const long slots = (long)n_sms * DT_BLOCKS_PER_SM;
+      const int blocks = (int)(n_items < slots ? n_items : slots);
+      if ((size_t)blocks * WARM_MAX_CHUNKS * SB_WARM_CHUNK < p.warm_bytes) p.warm_bytes = 0;
+      sb_launch<SB_K_ATTENTION>(attn_decode_tma_kernel, dim3(blocks), dim3(DT_THREADS), DT_SMEM, stream,
+                                map_kv, p, (int)n_items);
+      SB_CHECK_LAUNCH("sb_attention (decode, TMA)");
+      // Once: the kernel's tiles need shared memory that starts on a 1024-byte boundary, which it
+      // checks itself (status 10, nothing computed).  Should that ever be reported, this step and
+      // all later ones run on the earlier kernel.
+      static bool dt_checked = false;
+      cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+      if (!dt_checked && cudaStreamIsCapturing(stream, &cap) == cudaSuccess && cap == cudaStreamCaptureStatusNone) {
+        if (cudaStreamSynchronize(stream) != cudaSuccess)
+          SB_FAIL(SB_ERR_CUDA, "sb_attention: the persistent decode kernel failed");
+        dt_checked = true;
+        const int st = tc5_read_status();
+        if (st == 10) dt_misaligned = true;
+        else if (st != 0) SB_FAIL(SB_ERR_CUDA, "sb_attention: a wait in the decode kernel gave up (code %d)", st);
+      }
+      if (!dt_misaligned && p.n_splits > 1) {
+        sb_launch<SB_K_ATTENTION>(attn_merge_kernel, dim3(n_kv_heads, n_seqs), dim3(DT_MERGE_THREADS),
+                                  (size_t)2 * DEC_ROWS * p.n_splits * sizeof(float), stream, p);
+        SB_CHECK_LAUNCH("sb_attention (split merge)");
+        g_last_launches = 2;
+      }
+      if (!dt_misaligned) return SB_OK;
+    }
+#endif
     if ((size_t)p.n_splits * n_kv_heads * n_seqs * WARM_MAX_CHUNKS * SB_WARM_CHUNK < p.warm_bytes)
       p.warm_bytes = 0;
     sb_launch<SB_K_ATTENTION>(attn_decode_kernel, dim3(p.n_splits, n_kv_heads, n_seqs), dim3(DEC_WARPS * 32),
@@ -679,12 +742,13 @@ extern "C" int sb_attention(const void* q, void* out, int n_rows, int n_seqs, in
     return SB_OK;
   }
   p.n_splits = 1;
+  g_last_launches = 1;
 #ifdef SB_ATTN_TC5
   // tensor-memory kernel: needs the extent of the cache entry for its tensor map, row
   // coordinates that fit an int, and a positive scale (it takes the maximum before scaling)
   const long cache_rows = (long)n_pages * 2 * n_kv_heads * KT;
   static bool tc5_checked = false, tc5_misaligned = false;
-  if (n_pages > 0 && cache_rows < 2147483647L && scale > 0.0f && !g_force_mma && !tc5_misaligned) {
+  if (n_pages > 0 && cache_rows < 2147483647L && scale > 0.0f && g_force_mma != 1 && !tc5_misaligned) {
     static bool configured5 = false;
     if (!configured5) {
       cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc5_kernel,

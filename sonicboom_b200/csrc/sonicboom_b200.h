@@ -132,8 +132,9 @@ int sb_random_normal(void* out, int out_dtype, size_t n, uint32_t key0, uint32_t
 
 /* ------------------------------------------------------------------ attention library */
 int sb_attention_head_dim(void);
-void sb_attention_force_mma(int on);      /* 1: prefill always on the mma.sync kernel */
+void sb_attention_force_mma(int mode);    /* 0 by size; 1 the mma.sync kernels; 2 the TMA decode kernel always */
 int sb_attention_status(void);            /* as sb_tc5_status; -1: no tensor-memory kernel */
+int sb_attention_last_launches(void);     /* kernels the last sb_attention call launched */
 size_t sb_attention_scratch_bytes(int n_rows, int n_q_heads, int n_kv_heads, int max_new,
                                   int max_len);
 /* Causal grouped-query attention of a step's rows over one cache entry's pages (bfloat16). */

@@ -368,7 +368,9 @@ def attention(q: torch.Tensor, out: torch.Tensor, plan, group_index: int, cache:
 
     bfloat16 runs the tensor-core kernels (built for the head size at first use); float32, a
     head size those kernels do not take, or `kernel="plain"` run the plain kernel.  `"mma"` keeps
-    prefill on the mma.sync kernel where the tensor-memory kernel would run (head sizes 64, 128).
+    to the mma.sync kernels where the tensor-memory prefill kernel or the persistent TMA decode
+    kernel would run (head sizes 64, 128); `"tma"` runs that decode kernel whatever the number of
+    key splits (by itself it runs from about a wave of splits on).
     `warm`: a tensor the kernel after this one will stream (weights); the decode kernel asks for
     it into L2 while it merges its partial results.  A hint: it changes no result."""
     n = q.shape[0]
@@ -379,8 +381,8 @@ def attention(q: torch.Tensor, out: torch.Tensor, plan, group_index: int, cache:
         need = int(al.sb_attention_scratch_bytes(n, n_q_heads, n_kv_heads, plan.max_new, plan.max_len))
         scratch = plan.scratch(need, q.device)
         counters = _attn_counters(plan.n_seqs * n_kv_heads, q.device)
-        if kernel == "mma":
-            al.sb_attention_force_mma(1)
+        if kernel in ("mma", "tma"):
+            al.sb_attention_force_mma(1 if kernel == "mma" else 2)
         rc = al.sb_attention(
             _ptr(q), _ptr(out), n, plan.n_seqs, plan.max_new, _i32(plan.seq_row0, "seq_row0"),
             _i32(plan.seq_pos0, "seq_pos0"), _i32(g.page_off, "page_off"),
@@ -389,12 +391,12 @@ def attention(q: torch.Tensor, out: torch.Tensor, plan, group_index: int, cache:
             ctypes.c_size_t(scratch.numel() if scratch is not None else 0),
             _ptr(counters), counters.numel(), plan.max_len, cache.shape[0], _sm_count(q.device),
             *_warm_args(warm), _stream())
-        if kernel == "mma":
+        if kernel in ("mma", "tma"):
             al.sb_attention_force_mma(0)
         if rc != 0:
             raise KernelError(f"attention: {al.sb_last_error().decode()}")
         global LAUNCHES
-        LAUNCHES += 1
+        LAUNCHES += int(al.sb_attention_last_launches())
     else:
         _check(lib().sb_attention_plain(
             _ptr(q), _ptr(out), _code(q.dtype), n, _i32(plan.row_seq, "row_seq"),

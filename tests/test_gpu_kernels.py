@@ -253,10 +253,12 @@ def attention_ref(qkv, pos0, hq, hkv, hd, window, history=None, theta=10000.0, s
 @pytest.mark.parametrize("hq,hkv,hd", [(4, 2, 16), (6, 1, 32), (5, 5, 48), (14, 2, 64), (28, 4, 128),
                                        (3, 1, 80), (8, 8, 256)])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("kernel", ["plain", "auto", "mma"])
+@pytest.mark.parametrize("kernel", ["plain", "auto", "mma", "tma"])
 def test_rotation_cache_and_attention(hq, hkv, hd, dtype, kernel):
     if dtype == "float32" and kernel != "plain":
         pytest.skip("float32 has the plain kernel only")
+    if kernel == "tma" and hd not in (64, 128):
+        pytest.skip("the persistent decode kernel is written for head sizes 64 and 128")
     if kernel == "mma" and hd not in (64, 128):
         pytest.skip("auto already is the mma.sync kernel at this head size")
     tol = 1e-5 if dtype == "float32" else 1.5e-2
@@ -432,6 +434,75 @@ def test_decode_steps_after_a_long_prompt(hq, hkv, hd, window):
     assert ops.attention_status(hd) in (0, -1)            # -1: no tensor-memory kernel at this head size
 
 
+@pytest.mark.parametrize("hq,hkv,hd,window", [(28, 4, 128, 0), (14, 2, 64, 0), (8, 8, 128, 100), (6, 2, 64, 37),
+                                              (2, 1, 128, 0)])
+def test_persistent_decode_kernel(hq, hkv, hd, window):
+    """The persistent TMA decode kernel (forced: by itself it runs from about a wave of splits on):
+    sequences of 5 to 4,200 keys in one step, so one split and many, 256-key and 512-key splits,
+    a last tile with one key and with 64, three steps in a row; every row against the plain
+    implementation, and bit for bit against the same step run alone (nothing but a sequence's own
+    keys and length enters its result)."""
+    lens = [700, 300, 1025, 64, 5, 257, 4200, 191]
+    cache = make_cache(hkv, hd, window, torch.bfloat16, max_tokens=64 * 120)
+    xs = [torch.randn(n + 3, (hq + 2 * hkv) * hd, generator=torch.Generator().manual_seed(n)) for n in lens]
+    slots = [cache.open() for _ in lens]
+    run_attention(cache, hq, hkv, hd, window, torch.bfloat16, [(s, x[:n]) for s, x, n in zip(slots, xs, lens)])
+    alone = make_cache(hkv, hd, window, torch.bfloat16, max_tokens=64 * 70)
+    s_alone = alone.open()
+    run_attention(alone, hq, hkv, hd, window, torch.bfloat16, [(s_alone, xs[6][:lens[6]])])
+    for step in range(3):
+        out, _ = run_attention(cache, hq, hkv, hd, window, torch.bfloat16,
+                               [(s, x[n + step:n + step + 1]) for s, x, n in zip(slots, xs, lens)], kernel="tma")
+        for i, (x, n) in enumerate(zip(xs, lens)):
+            ref = attention_ref(x[n + step:n + step + 1], n + step, hq, hkv, hd, window, history=x[:n + step])
+            close(out[i:i + 1], ref, 1.5e-2)
+        one, _ = run_attention(alone, hq, hkv, hd, window, torch.bfloat16,
+                               [(s_alone, xs[6][lens[6] + step:lens[6] + step + 1])], kernel="tma")
+        assert torch.equal(one[0], out[6])
+    assert ops.attention_status(hd) == 0
+
+
+def test_persistent_decode_kernel_finds_a_key_wherever_it_lies():
+    """One key stands out; it lies in the first or the last tile of a split, in either half of a
+    tile (the warps of a pair), in an even or an odd tile (the pairs), in the only tile."""
+    hq, hkv, hd, n = 14, 2, 128, 901
+    for key_pos in (3, 40, 64, 100, 255, 256, 300, 511, 640, 767, 899):
+        cache = make_cache(hkv, hd, 0, torch.bfloat16)
+        x = standout(n, hq, hkv, hd, key_pos)
+        s = cache.open()
+        run_attention(cache, hq, hkv, hd, 0, torch.bfloat16, [(s, x[:n - 1])], rot=0)
+        out, _ = run_attention(cache, hq, hkv, hd, 0, torch.bfloat16, [(s, x[n - 1:])], rot=0, kernel="tma")
+        assert abs(float(out.mean()) - (key_pos + 1)) < 0.02 * (key_pos + 1), (key_pos, float(out.mean()))
+
+
+def test_many_sequences_reach_the_persistent_decode_kernel_by_themselves():
+    """64 sequences of 300 to 700 keys x 4 key/value heads x 3 splits: more splits than a wave of
+    the earlier kernel's blocks, so "auto" is the persistent kernel; its rows equal the forced
+    kernel's bit for bit, differ from the earlier kernel's by rounding only, and match the plain
+    implementation."""
+    hq, hkv, hd = 28, 4, 128
+    g = torch.Generator().manual_seed(5)
+    lens = torch.randint(300, 700, (64,), generator=g).tolist()
+    cache = make_cache(hkv, hd, 0, torch.bfloat16, max_tokens=64 * 12 * 64)
+    xs = [torch.randn(n + 1, (hq + 2 * hkv) * hd, generator=torch.Generator().manual_seed(n)) * 0.5 for n in lens]
+    slots = [cache.open() for _ in lens]
+    run_attention(cache, hq, hkv, hd, 0, torch.bfloat16, [(s, x[:n]) for s, x, n in zip(slots, xs, lens)])
+    step = [(s, x[n:]) for s, x, n in zip(slots, xs, lens)]
+    outs = {}
+    for kernel in ("auto", "tma", "mma"):
+        before = ops.LAUNCHES
+        outs[kernel], _ = run_attention(cache, hq, hkv, hd, 0, torch.bfloat16, step, kernel=kernel)
+        launched = ops.LAUNCHES - before
+        assert launched == (2 if kernel == "mma" else 3), (kernel, launched)     # rotation, attention (+ the split merge)
+        for s, n in zip(slots, lens):                 # the step is run three times: take it back
+            cache.truncate(s, n)
+    assert torch.equal(outs["auto"], outs["tma"])
+    assert not torch.equal(outs["auto"], outs["mma"]) and pm.rel_err(outs["auto"], outs["mma"]) < 1e-2
+    for i in (0, 17, 63):
+        ref = attention_ref(xs[i][lens[i]:], lens[i], hq, hkv, hd, 0, history=xs[i][:lens[i]])
+        close(outs["auto"][i:i + 1], ref, 1.5e-2)
+
+
 def test_decode_attention_across_the_split_length_change():
     """Splits are 256 keys up to a sequence length of 4,096 and 512 beyond.  A sequence that
     grows from 4,094 to 4,099 keys crosses the change, next to a short one in the same batch;
@@ -519,14 +590,15 @@ def test_sampled_tokens_do_not_depend_on_the_row():
 
 # ------------------------------------------------ positions outside a sequence's own pages
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("hq,hkv,hd,rows", [(4, 2, 16, 3), (28, 4, 128, 3), (4, 2, 16, 80)])
+@pytest.mark.parametrize("hq,hkv,hd,rows", [(4, 2, 16, 3), (28, 4, 128, 3), (4, 2, 16, 80), (8, 4, 64, 60)])
 def test_a_position_without_a_page_of_its_own_writes_and_reads_nothing(dtype, hq, hkv, hd, rows):
     """Rows whose position lies beyond their sequence's page list (a plan that a finished row of
     a captured batch would reach if nothing stopped it), or before 0: the rotation kernel writes
     no key or value for them, the attention gives them rows of zeros, every other sequence's
     pages stay as they were, and the neighbours' results are what they are without them.  All
-    three forms of the rotation kernel (per head, per row, vector) and the decode attention's
-    merge counters are covered: a second, ordinary step right after gives the right result."""
+    three forms of the rotation kernel (per head, per row, vector), the decode attention's merge
+    counters and (60 sequences x 4 heads x 2 splits) the persistent decode kernel are covered: a
+    second, ordinary step right after gives the right result."""
     dt = DT[dtype]
     cache = make_cache(hkv, hd, 0, dt, max_tokens=64 * 7 * rows)
     storage = cache.groups[0].entry_storage(0)
