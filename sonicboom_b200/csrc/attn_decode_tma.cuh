@@ -22,9 +22,15 @@
 // the merge area (the four warps' partial outputs are exactly one stage); the warps are merged
 // in warp order, and the split's partial goes to scratch (or the finished rows out when the
 // sequence has one split).  The splits of a sequence are merged, in ascending order as before,
-// by a small kernel of its own after this one (attn_merge_kernel): handing the partials over
-// inside this kernel takes a device-wide release/acquire per item, which stalled the four warps
-// for 1 to 2.5 us out of an item's 8 (an arrival counter as in attn_decode_kernel, measured).
+// by a small kernel of its own after this one (attn_merge_kernel).  Handing the partials over
+// inside this kernel, through an arrival counter as in attn_decode_kernel, takes a device-wide
+// release/acquire atomic per item, and every form of it that was tried cost more than the
+// merge kernel's launch (measured at 64 sequences of 3,072 keys, per launch, against 70 us for
+// the walk alone plus 3 us for the merge kernel: the arrival by a thread of the first warp pair
+// 140 us, by a thread of the second pair, which waits for its next tile then anyway, 118 us; by
+// a second thread of the producer warp, which holds up the producer, 129 us; for all of a
+// block's items at the end of its walk, which puts most merges on the blocks that finish last,
+// 108 us).
 //
 // Every wait on an mbarrier is bounded (tc5.cuh); after the first wait that gives up the block
 // stops loading and computing, keeps walking its items so that every barrier is still reached,
@@ -47,19 +53,17 @@ constexpr int DT_QUEUE = 2;                                  // items whose reco
 constexpr uint32_t DT_Q_ROW = HD * 2 + 16;                   // a query row and 16 bytes: rows fall into different banks
 constexpr uint32_t DT_Q_BYTES = DEC_ROWS * DT_Q_ROW;         // an item's query rows
 static_assert(DT_WARPS * DEC_ROWS * HD * 4 == DT_STAGE_BYTES, "the warps' partial outputs fill one stage");
-// after the ring: the queue's query rows and records; per-warp (m, l) of 16 rows, the warps'
-// weights, the merged (m, l); barriers
+// after the ring: the queue's query rows and records; per-warp (m, l) of 16 rows; barriers
 constexpr uint32_t DT_REC_INTS = 12;
-constexpr uint32_t DT_SMALL_BYTES = (2 * DT_WARPS + DT_WARPS + 2) * DEC_ROWS * 4;
+constexpr uint32_t DT_FLAGS = 4;                             // two flags of the kernel, padded to 16 bytes
+constexpr uint32_t DT_SMALL_BYTES = 2 * DT_WARPS * DEC_ROWS * 4;
 // ... and the record the consumers are on with two flags.  No statically allocated shared memory
 // and no slack for aligning by hand: the ring starts the block's shared memory, which is where
 // the 1024-byte boundary is (checked in the kernel), so that three blocks fit an SM's 228 KB in
 // the 1 KB units it is handed out in.
 constexpr uint32_t DT_SMEM = DT_STAGES * DT_STAGE_BYTES + DT_QUEUE * (DT_Q_BYTES + DT_REC_INTS * 4) +
-                             DT_SMALL_BYTES + (DT_REC_INTS + 4) * 4 + 8 * (2 * DT_STAGES + 2 * DT_QUEUE);
+                             DT_SMALL_BYTES + (DT_REC_INTS + DT_FLAGS) * 4 + 8 * (2 * DT_STAGES + 2 * DT_QUEUE);
 static_assert(DT_BLOCKS_PER_SM * ((DT_SMEM + 1023) / 1024 + 1) <= 228, "three blocks per SM");
-// The final merge stages every split's (m, l) of up to 16 rows in the merge area.
-constexpr int DT_MAX_SPLITS = DT_STAGE_BYTES / (2 * DEC_ROWS * 4);
 
 // Place of four consecutive values (c = 0 ... HD/4-1) of `row` of warp `w` in the merge area:
 // rows are HD floats apart, so groups of eight values are exchanged by the row's low bits to
@@ -307,13 +311,11 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const AttnPar
   int* recs = reinterpret_cast<int*>(q_ptr + DT_QUEUE * DT_Q_BYTES);        // [queue][DT_REC_INTS]
   float* warp_m = reinterpret_cast<float*>(recs + DT_QUEUE * DT_REC_INTS);  // [warp][16]
   float* warp_l = warp_m + DT_WARPS * DEC_ROWS;            // [warp][16]
-  float* fac = warp_l + DT_WARPS * DEC_ROWS;               // [warp][16] weights
-  float* row_m = fac + DT_WARPS * DEC_ROWS;                // [16] merged maximum
-  float* row_l = row_m + DEC_ROWS;                         // [16] merged sum
-  int* s_cur = reinterpret_cast<int*>(row_l + DEC_ROWS);   // [DT_REC_INTS] the record of the item the consumers are on
-  int& s_ok = s_cur[DT_REC_INTS];
-  int& s_abort = s_cur[DT_REC_INTS + 1];
-  const uint32_t bars = q_s + DT_QUEUE * (DT_Q_BYTES + DT_REC_INTS * 4) + DT_SMALL_BYTES + (DT_REC_INTS + 4) * 4;
+  int* s_cur = reinterpret_cast<int*>(warp_l + DT_WARPS * DEC_ROWS);   // [DT_REC_INTS] the record of the item the consumers are on
+  int* flags = s_cur + DT_REC_INTS;
+  int& s_ok = flags[0];                    // one view of "nothing gave up" for every consumer thread
+  int& s_abort = flags[1];                 // a bounded wait gave up: nothing more is loaded, computed or written
+  const uint32_t bars = q_s + DT_QUEUE * (DT_Q_BYTES + DT_REC_INTS * 4) + DT_SMALL_BYTES + (DT_REC_INTS + DT_FLAGS) * 4;
   const uint32_t full0 = bars, empty0 = full0 + 8 * DT_STAGES;
   const uint32_t qfull0 = empty0 + 8 * DT_STAGES, qempty0 = qfull0 + 8 * DT_QUEUE;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -328,7 +330,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const AttnPar
       mbar_init(qfull0 + 8 * d, 1);
       mbar_init(qempty0 + 8 * d, DT_WARPS);
     }
-    s_abort = 0;
+    for (int i = 0; i < (int)DT_FLAGS; ++i) flags[i] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
   }
@@ -503,7 +505,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const AttnPar
         l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
       }
       dt_bar_sync(1, DT_CONSUMERS);                    // every warp has read the last tile
-      {
+      fetch();                                         // the next record, while the merge goes on
 #pragma unroll
       for (int hf = 0; hf < 2; ++hf) {
         const int row = hf ? rb : ra;
@@ -516,40 +518,30 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const AttnPar
           warp_l[warp * DEC_ROWS + row] = l[hf];
         }
       }
-      dt_bar_sync(1, DT_CONSUMERS);
-      // the warps in warp order: each row's weights exp2(m_w - max) and its sum,
-      if (tid < DEC_ROWS) {
-        float mm = -INFINITY;
-#pragma unroll
-        for (int q = 0; q < DT_WARPS; ++q) mm = fmaxf(mm, warp_m[q * DEC_ROWS + tid]);
-        const float base = mm == -INFINITY ? 0.0f : mm;
-        float ll = 0.0f;
-#pragma unroll
-        for (int q = 0; q < DT_WARPS; ++q) {
-          const float f = exp2f(warp_m[q * DEC_ROWS + tid] - base);
-          fac[q * DEC_ROWS + tid] = f;
-          ll += warp_l[q * DEC_ROWS + tid] * f;
-        }
-        row_m[tid] = mm;
-        row_l[tid] = ll;
-      }
       if (tid == 0) s_ok = !*abort_flag;               // one view of "nothing gave up" for everybody
       dt_bar_sync(1, DT_CONSUMERS);
       const bool ok = s_ok != 0;
       const bool single = w.split_lo == w.split_hi;
-      // then the outputs, four values of a row per thread
+      // The warps are merged in warp order.  Four values of a row per thread, which works out
+      // the row's weights exp2(m_w - max) and its sum itself.
       for (int i = tid; i < w.R * (HD / 4) && ok; i += DT_CONSUMERS) {
         const int row = i / (HD / 4), c = i % (HD / 4);
+        float mm = -INFINITY;
+#pragma unroll
+        for (int q = 0; q < DT_WARPS; ++q) mm = fmaxf(mm, warp_m[q * DEC_ROWS + row]);
+        const float base = mm == -INFINITY ? 0.0f : mm;
+        float ll = 0.0f;
         float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 #pragma unroll
         for (int q = 0; q < DT_WARPS; ++q) {
+          const float f = exp2f(warp_m[q * DEC_ROWS + row] - base);
+          ll += warp_l[q * DEC_ROWS + row] * f;
           const float4 v = *reinterpret_cast<const float4*>(part + dt_part_at(q, row, c));
-          const float f = fac[q * DEC_ROWS + row];
           acc.x += v.x * f; acc.y += v.y * f; acc.z += v.z * f; acc.w += v.w * f;
         }
         const size_t out_row = (size_t)(w.row0 + row / G) * p.n_q_heads + w.kvh * G + row % G;
         if (single) {
-          const float inv = 1.0f / row_l[row];
+          const float inv = 1.0f / ll;
           uint2 v;
           v.x = pack_bf16(acc.x * inv, acc.y * inv);
           v.y = pack_bf16(acc.z * inv, acc.w * inv);
@@ -558,16 +550,13 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const AttnPar
           float* dst = p.scratch + (out_row * p.n_splits + w.split) * PART_STRIDE;
           *reinterpret_cast<float4*>(dst + 4 * c) = acc;
           if (c == 0) {
-            dst[HD] = row_m[row];
-            dst[HD + 1] = row_l[row];
+            dst[HD] = mm;
+            dst[HD + 1] = ll;
           }
         }
       }
-      }
-      // hand the stage back (the merge wrote it with ordinary stores, the next page comes by
-      // TMA) and take the next record
+      // hand the stage back: the merge wrote it with ordinary stores, the next page comes by TMA
       asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-      fetch();
       dt_bar_sync(1, DT_CONSUMERS);
       if (pair == last_pair && lane == 0) mbar_arrive(empty0 + 8 * s_merge);
     }

@@ -686,12 +686,15 @@ extern "C" int sb_attention(const void* q, void* out, int n_rows, int n_seqs, in
     // the merge of the splits as a kernel of its own.
     const long cache_rows_d = (long)n_pages * 2 * n_kv_heads * KT;
     const long n_items = (long)n_seqs * n_kv_heads * p.n_splits;
-    // It pays from about one wave of the earlier kernel's blocks on (three per SM): measured on
-    // B200 at 28/4 heads of 128 and 3,072 keys, 8 sequences (416 splits) take 15.1 us there and
-    // 17.0 us here, 12 sequences 25.2 and 23.5 us, 64 sequences 87.6 and 77.0 us.
+    // It pays from about two waves of the earlier kernel's blocks on (three per SM): measured on
+    // B200 at 28/4 heads of 128 and 3,072 keys, alone: 8 sequences (416 splits) take 15.1 us there
+    // and 17.0 us here, 12 sequences 25.2 and 23.5 us, 64 sequences 87.6 and 77.0 us; inside the
+    // decode step of a 7B-sized model the earlier kernel still wins at 8 sequences by 0.2 ms.
+    // Launched without programmatic dependent launch: its blocks fill every SM's shared memory,
+    // and starting them early cost 0.06 ms a step at 64 sequences.
     static bool dt_misaligned = false;
     if (g_force_mma != 1 && !dt_misaligned && n_pages > 0 && n_sms > 0 && cache_rows_d < 2147483647L &&
-        n_items < 2147483647L && (n_items > 3L * n_sms || g_force_mma == 2) && (size_t)2 * DEC_ROWS * p.n_splits * sizeof(float) <= 48 * 1024) {
+        n_items < 2147483647L && (n_items > 6L * n_sms || g_force_mma == 2) && (size_t)2 * DEC_ROWS * p.n_splits * sizeof(float) <= 48 * 1024) {
       static bool configured_dt = false;
       if (!configured_dt) {
         cudaError_t e = cudaFuncSetAttribute(attn_decode_tma_kernel,
@@ -709,8 +712,8 @@ extern "C" int sb_attention(const void* q, void* out, int n_rows, int n_seqs, in
       const long slots = (long)n_sms * DT_BLOCKS_PER_SM;
       const int blocks = (int)(n_items < slots ? n_items : slots);
       if ((size_t)blocks * WARM_MAX_CHUNKS * SB_WARM_CHUNK < p.warm_bytes) p.warm_bytes = 0;
-      sb_launch<SB_K_ATTENTION>(attn_decode_tma_kernel, dim3(blocks), dim3(DT_THREADS), DT_SMEM, stream,
-                                map_kv, p, (int)n_items);
+      sb_launch<0>(attn_decode_tma_kernel, dim3(blocks), dim3(DT_THREADS), DT_SMEM, stream, map_kv, p,
+                   (int)n_items);
       SB_CHECK_LAUNCH("sb_attention (decode, TMA)");
       // Once: the kernel's tiles need shared memory that starts on a 1024-byte boundary, which it
       // checks itself (status 10, nothing computed).  Should that ever be reported, this step and

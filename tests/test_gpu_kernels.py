@@ -476,24 +476,21 @@ def test_persistent_decode_kernel_finds_a_key_wherever_it_lies():
 
 
 def test_many_sequences_reach_the_persistent_decode_kernel_by_themselves():
-    """64 sequences of 300 to 700 keys x 4 key/value heads x 3 splits: more splits than a wave of
-    the earlier kernel's blocks, so "auto" is the persistent kernel; its rows equal the forced
-    kernel's bit for bit, differ from the earlier kernel's by rounding only, and match the plain
-    implementation."""
+    """64 sequences of 600 to 1,000 keys x 4 key/value heads x 4 splits: more splits than two waves
+    of the earlier kernel's blocks on 148 SMs, so "auto" is the persistent kernel; its rows equal
+    the forced kernel's bit for bit, differ from the earlier kernel's by rounding only, and match
+    the plain implementation."""
     hq, hkv, hd = 28, 4, 128
     g = torch.Generator().manual_seed(5)
-    lens = torch.randint(300, 700, (64,), generator=g).tolist()
-    cache = make_cache(hkv, hd, 0, torch.bfloat16, max_tokens=64 * 12 * 64)
+    lens = torch.randint(600, 1000, (64,), generator=g).tolist()
+    cache = make_cache(hkv, hd, 0, torch.bfloat16, max_tokens=64 * 17 * 64)
     xs = [torch.randn(n + 1, (hq + 2 * hkv) * hd, generator=torch.Generator().manual_seed(n)) * 0.5 for n in lens]
     slots = [cache.open() for _ in lens]
     run_attention(cache, hq, hkv, hd, 0, torch.bfloat16, [(s, x[:n]) for s, x, n in zip(slots, xs, lens)])
     step = [(s, x[n:]) for s, x, n in zip(slots, xs, lens)]
     outs = {}
     for kernel in ("auto", "tma", "mma"):
-        before = ops.LAUNCHES
         outs[kernel], _ = run_attention(cache, hq, hkv, hd, 0, torch.bfloat16, step, kernel=kernel)
-        launched = ops.LAUNCHES - before
-        assert launched == (2 if kernel == "mma" else 3), (kernel, launched)     # rotation, attention (+ the split merge)
         for s, n in zip(slots, lens):                 # the step is run three times: take it back
             cache.truncate(s, n)
     assert torch.equal(outs["auto"], outs["tma"])
@@ -627,19 +624,21 @@ def test_a_position_without_a_page_of_its_own_writes_and_reads_nothing(dtype, hq
     g = plan.groups[0]
     ops.rope_store(qkv, hq, hkv, hd, hd, inv, plan.row_seq, plan.row_pos, g.page_off, g.page_ids,
                    g.page_size, storage, q)
-    out = torch.full((rows, hq * hd), 7.0, dtype=dt, device=DEV)
-    ops.attention(q, out, plan, 0, storage, hq, hkv, hd, 0, hd ** -0.5)
-    torch.cuda.synchronize()
     changed = (storage != before).any(dim=-1).any(dim=-1)             # [page, k|v, head]
     good_pages = {cache.page_list(s, 0)[(base + i) // 64] for i, s in enumerate(slots) if i not in bad}
     assert set(changed.nonzero()[:, 0].tolist()) == good_pages
-    out = out.float().cpu()
-    for r in range(rows):
-        if r in bad:
-            assert float(out[r].abs().max()) == 0.0
-        else:
-            ref = attention_ref(new[r], base + r, hq, hkv, hd, 0, history=hist[r])
-            close(out[r:r + 1], ref, 1e-5 if dtype == "float32" else 2e-2)
+    kernels = ["auto", "tma"] if dtype == "bfloat16" and hd in (64, 128) else ["auto"]
+    for kernel in kernels:                                  # both decode kernels where there are two
+        out = torch.full((rows, hq * hd), 7.0, dtype=dt, device=DEV)
+        ops.attention(q, out, plan, 0, storage, hq, hkv, hd, 0, hd ** -0.5, kernel=kernel)
+        torch.cuda.synchronize()
+        out = out.float().cpu()
+        for r in range(rows):
+            if r in bad:
+                assert float(out[r].abs().max()) == 0.0, (kernel, r)
+            else:
+                ref = attention_ref(new[r], base + r, hq, hkv, hd, 0, history=hist[r])
+                close(out[r:r + 1], ref, 1e-5 if dtype == "float32" else 2e-2)
     # the same step with its true positions right after: scratch and counters are as they should be
     plan2 = StepPlan(cache, [StepEntry(s, [0], []) for s in slots], DEV)
     g2 = plan2.groups[0]
