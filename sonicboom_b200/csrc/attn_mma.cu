@@ -686,15 +686,18 @@ extern "C" int sb_attention(const void* q, void* out, int n_rows, int n_seqs, in
     // the merge of the splits as a kernel of its own.
     const long cache_rows_d = (long)n_pages * 2 * n_kv_heads * KT;
     const long n_items = (long)n_seqs * n_kv_heads * p.n_splits;
-    // It pays from about two waves of the earlier kernel's blocks on (three per SM): measured on
-    // B200 at 28/4 heads of 128 and 3,072 keys, alone: 8 sequences (416 splits) take 15.1 us there
-    // and 17.0 us here, 12 sequences 25.2 and 23.5 us, 64 sequences 87.6 and 77.0 us; inside the
-    // decode step of a 7B-sized model the earlier kernel still wins at 8 sequences by 0.2 ms.
-    // Launched without programmatic dependent launch: its blocks fill every SM's shared memory,
-    // and starting them early cost 0.06 ms a step at 64 sequences.
+    // It pays when there are many splits.  Measured on B200 at 28/4 heads of 128 and 3,072 keys,
+    // the kernels alone (this one with its merge kernel): 8 sequences 15.1 us the earlier kernel
+    // and 17.0 us this one, 12 sequences 25.2 and 23.5 us, 32 sequences 48.7 and 44.0 us, 64
+    // sequences 87.6 and 77.9 us.  Inside the decode step of a 7B-sized model, where the earlier
+    // kernel's many short blocks overlap the kernels around them better and the merge kernel is
+    // one more launch: 32 sequences 4.24 and 4.28 ms a step, 64 sequences 5.93 and 5.68 ms.  So
+    // from twenty blocks' worth of splits per SM on.  Launched without programmatic dependent
+    // launch: its blocks fill every SM's shared memory, and starting them early cost 0.06 ms a
+    // step at 64 sequences.
     static bool dt_misaligned = false;
     if (g_force_mma != 1 && !dt_misaligned && n_pages > 0 && n_sms > 0 && cache_rows_d < 2147483647L &&
-        n_items < 2147483647L && (n_items > 6L * n_sms || g_force_mma == 2) && (size_t)2 * DEC_ROWS * p.n_splits * sizeof(float) <= 48 * 1024) {
+        n_items < 2147483647L && (n_items > 20L * n_sms || g_force_mma == 2) && (size_t)2 * DEC_ROWS * p.n_splits * sizeof(float) <= 48 * 1024) {
       static bool configured_dt = false;
       if (!configured_dt) {
         cudaError_t e = cudaFuncSetAttribute(attn_decode_tma_kernel,

@@ -355,7 +355,10 @@ def attention_lib(head_dim: int):
     outside what those kernels are written for (multiples of 16 up to 256)."""
     if head_dim not in _attn_libs:
         if head_dim in _build.HEAD_DIMS:
-            _attn_libs[head_dim] = _abi.apply(_build.load_attention(head_dim), _abi.ATTENTION)
+            al = _abi.apply(_build.load_attention(head_dim), _abi.ATTENTION)
+            # SB_ATTN=mma|tma in the environment: one kernel family for every step (for measurements)
+            al.sb_attention_force_mma({"mma": 1, "tma": 2}.get(_os.environ.get("SB_ATTN", ""), 0))
+            _attn_libs[head_dim] = al
         else:
             _attn_libs[head_dim] = None
     return _attn_libs[head_dim]
@@ -392,7 +395,7 @@ def attention(q: torch.Tensor, out: torch.Tensor, plan, group_index: int, cache:
             _ptr(counters), counters.numel(), plan.max_len, cache.shape[0], _sm_count(q.device),
             *_warm_args(warm), _stream())
         if kernel in ("mma", "tma"):
-            al.sb_attention_force_mma(0)
+            al.sb_attention_force_mma({"mma": 1, "tma": 2}.get(_os.environ.get("SB_ATTN", ""), 0))
         if rc != 0:
             raise KernelError(f"attention: {al.sb_last_error().decode()}")
         global LAUNCHES

@@ -476,14 +476,15 @@ def test_persistent_decode_kernel_finds_a_key_wherever_it_lies():
 
 
 def test_many_sequences_reach_the_persistent_decode_kernel_by_themselves():
-    """64 sequences of 600 to 1,000 keys x 4 key/value heads x 4 splits: more splits than two waves
-    of the earlier kernel's blocks on 148 SMs, so "auto" is the persistent kernel; its rows equal
-    the forced kernel's bit for bit, differ from the earlier kernel's by rounding only, and match
-    the plain implementation."""
-    hq, hkv, hd = 28, 4, 128
+    """96 sequences x 4 key/value heads x 8 splits (one sequence of 1,900 keys sizes the grid, the
+    others have 100 to 700): more than twenty splits per SM on 148 SMs, so "auto" is the
+    persistent kernel, which finds most of its work items empty; its rows equal the forced
+    kernel's bit for bit, differ from the earlier kernel's by rounding only, and match the plain
+    implementation."""
+    hq, hkv, hd = 8, 4, 128
     g = torch.Generator().manual_seed(5)
-    lens = torch.randint(600, 1000, (64,), generator=g).tolist()
-    cache = make_cache(hkv, hd, 0, torch.bfloat16, max_tokens=64 * 17 * 64)
+    lens = [1900] + torch.randint(100, 700, (95,), generator=g).tolist()
+    cache = make_cache(hkv, hd, 0, torch.bfloat16, max_tokens=(31 + 95 * 12) * 64)
     xs = [torch.randn(n + 1, (hq + 2 * hkv) * hd, generator=torch.Generator().manual_seed(n)) * 0.5 for n in lens]
     slots = [cache.open() for _ in lens]
     run_attention(cache, hq, hkv, hd, 0, torch.bfloat16, [(s, x[:n]) for s, x, n in zip(slots, xs, lens)])
@@ -495,7 +496,7 @@ def test_many_sequences_reach_the_persistent_decode_kernel_by_themselves():
             cache.truncate(s, n)
     assert torch.equal(outs["auto"], outs["tma"])
     assert not torch.equal(outs["auto"], outs["mma"]) and pm.rel_err(outs["auto"], outs["mma"]) < 1e-2
-    for i in (0, 17, 63):
+    for i in (0, 17, 95):
         ref = attention_ref(xs[i][lens[i]:], lens[i], hq, hkv, hd, 0, history=xs[i][:lens[i]])
         close(outs["auto"][i:i + 1], ref, 1.5e-2)
 
