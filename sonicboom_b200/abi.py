@@ -36,6 +36,7 @@ CORE = {
     "sb_gemm_tc5_ex": ("i", _GEMM[:-1] + "pziips"),
     "sb_gemm_tc5_scratch_bytes": ("z", "iiii"),
     "sb_gemm_tc5_fuses_norm": ("i", "iiiiiii"),
+    "sb_gemm_tc5_fuses_rope": ("i", "iiiiiiiii"),
     "sb_tc5_status": ("i", ""),
     "sb_attention_plain": ("i", "ppiippppipiiiiifs"),
     "sb_sample_params_size": ("i", ""),

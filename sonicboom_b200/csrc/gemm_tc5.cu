@@ -465,6 +465,99 @@ tc5_reduce_kernel(const Tc5Params p, int bn) {
   }
 }
 
+// The same sum for a fused q|k|v product, followed by the rotation and the cache write that
+// rope_store_vec_kernel (elementwise.cu) does on the finished row: the float32 row is neither
+// written nor read again, and the step has one kernel less.  The same sums in the same order and
+// the same rotation formulas as the two kernels.  A block takes a
+// token and a share of its heads; a task is four pairs (e, e + half) of one head, or four of the
+// values beyond the rotated part.  cos and sin of the token's position are worked out once a
+// block (from the step's plan, before the wait for the product).
+constexpr int RR_THREADS = 256, RR_HEAD_SHARES = 4;
+__global__ void __launch_bounds__(RR_THREADS)
+tc5_reduce_rope_kernel(const Tc5Params p, int bn, const SbRopeStore r) {
+  extern __shared__ float rr_cs[];                   // cos[rot/2], then sin[rot/2]
+  sb_pdl_launch();
+  const int t = blockIdx.x;
+  const int pos = r.row_pos[t];
+  const int half = r.rot >> 1, hd = r.hd;
+  for (int i = threadIdx.x; i < half; i += RR_THREADS) {
+    const float theta = (float)pos * r.inv_freq[i];
+    rr_cs[i] = cosf(theta);
+    rr_cs[half + i] = sinf(theta);
+  }
+  const bool has_kv = r.cache != nullptr;
+  const int n_heads = r.n_q_heads + (has_kv ? 2 * r.n_kv_heads : 0);
+  size_t k_base = 0, v_base = 0;
+  bool stores = has_kv;
+  if (has_kv) {
+    // a position without a page in its own sequence's list writes no key and no value
+    const int seq = r.row_seq[t], first = r.page_off[seq], n_pages = r.page_off[seq + 1] - first;
+    const int pi = pos / r.page_size;
+    const int page = (pos >= 0 && pi < n_pages) ? r.page_ids[first + pi] : -1;
+    stores = page >= 0;
+    k_base = (((size_t)(stores ? page : 0) * 2) * r.n_kv_heads * r.page_size + pos % r.page_size) * hd;
+    v_base = (((size_t)(stores ? page : 0) * 2 + 1) * r.n_kv_heads * r.page_size + pos % r.page_size) * hd;
+  }
+  __syncthreads();
+  sb_pdl_wait();
+  const int pair_tasks = half >> 2, per_head = pair_tasks + ((hd - r.rot) >> 2);
+  const int heads_per = (n_heads + RR_HEAD_SHARES - 1) / RR_HEAD_SHARES;
+  const int head_lo = blockIdx.y * heads_per, head_hi = min(n_heads, head_lo + heads_per);
+  bf16* q_out = (bf16*)r.q_out;
+  bf16* cache = (bf16*)r.cache;
+  // the sum over the splits of four consecutive features starting at feature n of token t, + bias
+  auto sum4 = [&](int n, float (&acc)[4]) {
+    const int tile = n / BM, f = n % BM;
+    const float* base = p.scratch + (((size_t)tile * p.k_splits) * bn + t) * BM + f;
+    acc[0] = acc[1] = acc[2] = acc[3] = 0.0f;
+    for (int s = 0; s < p.k_splits; ++s) {
+      const float4 v = *reinterpret_cast<const float4*>(base + (size_t)s * bn * BM);
+      acc[0] += v.x; acc[1] += v.y; acc[2] += v.z; acc[3] += v.w;
+    }
+    if (p.epilogue == SB_EPI_BIAS) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        acc[i] += p.bias_dtype == SB_F32 ? bias_at<float>(p.bias, n + i) : bias_at<bf16>(p.bias, n + i);
+    }
+  };
+  auto store4 = [](bf16* dst, float a, float b, float c, float d) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    uint2 v;
+    v.x = *reinterpret_cast<uint32_t*>(&lo);
+    v.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(dst) = v;
+  };
+  for (int task = threadIdx.x; task < (head_hi - head_lo) * per_head; task += RR_THREADS) {
+    const int head = head_lo + task / per_head, k = task % per_head;      // q heads, then k heads, then v heads
+    const bool is_v = head >= r.n_q_heads + r.n_kv_heads;
+    if (head >= r.n_q_heads && !stores) continue;
+    bf16* dst = head < r.n_q_heads ? q_out + ((size_t)t * r.n_q_heads + head) * hd
+                : is_v ? cache + v_base + (size_t)(head - r.n_q_heads - r.n_kv_heads) * r.page_size * hd
+                       : cache + k_base + (size_t)(head - r.n_q_heads) * r.page_size * hd;
+    float a[4], b[4];
+    if (k >= pair_tasks) {                           // beyond the rotated part: a copy
+      const int e = r.rot + 4 * (k - pair_tasks);
+      sum4(head * hd + e, a);
+      store4(dst + e, a[0], a[1], a[2], a[3]);
+      continue;
+    }
+    const int e = 4 * k;
+    sum4(head * hd + e, a);
+    sum4(head * hd + e + half, b);
+    if (is_v) {
+      store4(dst + e, a[0], a[1], a[2], a[3]);
+      store4(dst + e + half, b[0], b[1], b[2], b[3]);
+    } else {
+      const float4 c = *reinterpret_cast<const float4*>(rr_cs + e);
+      const float4 sn = *reinterpret_cast<const float4*>(rr_cs + half + e);
+      store4(dst + e, a[0] * c.x - b[0] * sn.x, a[1] * c.y - b[1] * sn.y, a[2] * c.z - b[2] * sn.z,
+             a[3] * c.w - b[3] * sn.w);
+      store4(dst + e + half, a[0] * sn.x + b[0] * c.x, a[1] * sn.y + b[1] * c.y, a[2] * sn.z + b[2] * c.z,
+             a[3] * sn.w + b[3] * c.w);
+    }
+  }
+}
+
 // The same sum for a row-wise epilogue, followed by the RMSNorm of the finished rows: what a
 // pre-norm block's next product reads.  A cluster of RN_CLUSTER blocks takes one token; a block
 // adds the partial tiles of its part of the row, writes the float32 result, and the blocks
@@ -693,13 +786,40 @@ extern "C" int sb_gemm_tc5_fuses_norm(int M, int N, int K, int n_sms, int epilog
   return norm_fuses(M, N, K, n_sms, epilogue, out_dtype, form) ? 1 : 0;
 }
 
+// Whether the swapped split-K form can finish these rows with the rotation and the cache write.
+static bool rope_fuses(int M, int N, int K, int n_sms, int n_q_heads, int n_kv_heads, int hd, int rot,
+                       int has_kv) {
+  if (M <= 0 || M > 64 || N <= 0 || K <= 0 || n_q_heads <= 0 || hd <= 0 || (has_kv && n_kv_heads <= 0)) return false;
+  if (N != (n_q_heads + (has_kv ? 2 * n_kv_heads : 0)) * hd) return false;
+  if (rot < 0 || rot > hd || (rot & 7) || ((hd - rot) & 3) || (hd & 3)) return false;
+  return choose_splits(N, K, n_sms) > 1;
+}
+
+extern "C" int sb_gemm_tc5_fuses_rope(int M, int N, int K, int n_sms, int n_q_heads, int n_kv_heads,
+                                      int hd, int rot, int has_kv) {
+  return rope_fuses(M, N, K, n_sms, n_q_heads, n_kv_heads, hd, rot, has_kv) ? 1 : 0;
+}
+
 static int tc5_run(const void* A, int a_dtype, const void* W, int w_dtype, int M, int N,
                    int K, int epilogue, const void* bias, int bias_dtype,
                    const float* residual, void* out, int out_dtype, void* scratch,
                    size_t scratch_bytes, int n_sms, int form, const SbLinearExtras* extras,
                    cudaStream_t stream) {
   const SbLinearExtras* norm = extras && extras->norm_weight ? extras : nullptr;
-  if (int rc = sb_check_linear_args("sb_gemm_tc5", M, N, K, epilogue, bias, residual, out_dtype))
+  const SbRopeStore* rope = extras ? extras->rope : nullptr;
+  if (rope) {
+    // the product's rows go through the rotation into q_out and the cache; `out` is not written
+    if (norm || (epilogue != SB_EPI_BIAS && epilogue != SB_EPI_NONE) || form == 1 ||
+        !rope_fuses(M, N, K, n_sms, rope->n_q_heads, rope->n_kv_heads, rope->hd, rope->rot, rope->cache != nullptr))
+      SB_FAIL(SB_ERR_UNSUPPORTED, "sb_gemm_tc5: these sizes do not take the fused rotation "
+              "(see sb_gemm_tc5_fuses_rope)");
+    if (!rope->q_out || !rope->inv_freq || !rope->row_pos || (rope->cache && (!rope->row_seq || !rope->page_off ||
+        !rope->page_ids || rope->page_size <= 0)))
+      SB_FAIL(SB_ERR_ARG, "sb_gemm_tc5: rotation arguments missing");
+    if ((((uintptr_t)rope->q_out | (uintptr_t)rope->cache) & 7) || ((uintptr_t)rope->inv_freq & 15))
+      SB_FAIL(SB_ERR_ARG, "sb_gemm_tc5: unaligned rotation operands");
+    if (epilogue == SB_EPI_BIAS && !bias) SB_FAIL(SB_ERR_ARG, "sb_gemm_tc5: bias epilogue without a bias");
+  } else if (int rc = sb_check_linear_args("sb_gemm_tc5", M, N, K, epilogue, bias, residual, out_dtype))
     return rc;
   if (norm) {
     if (epilogue == SB_EPI_SWIGLU || out_dtype != SB_F32)
@@ -795,6 +915,13 @@ static int tc5_run(const void* A, int a_dtype, const void* W, int w_dtype, int M
   else { SB_TC5_SWAPPED(64, 4) }
 #undef SB_TC5_SWAPPED
   if (rc != SB_OK || splits <= 1) return rc;
+  if (rope) {
+    const size_t smem = (size_t)(rope->rot > 0 ? rope->rot : 2) * sizeof(float);
+    sb_launch<SB_K_REDUCE>(tc5_reduce_rope_kernel, dim3((unsigned)M, RR_HEAD_SHARES), dim3(RR_THREADS), smem,
+                           stream, p, bn, *rope);
+    SB_CHECK_LAUNCH("sb_gemm_tc5 (reduce + rotation)");
+    return SB_OK;
+  }
   if (norm) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(RN_CLUSTER, (unsigned)M);

@@ -47,8 +47,23 @@ enum SbKernelClass {
   SB_K_OTHER = 32        /* sampler, plain kernels */
 };
 
-/* What may accompany a product (all optional): the RMSNorm of its finished rows, and memory to
- * ask into L2 for a later kernel. */
+/* The rotation and cache write that may finish a fused q|k|v product (the arguments of
+ * sb_rope_store without the input row, which the product supplies). */
+typedef struct SbRopeStore {
+  int n_q_heads, n_kv_heads, hd, rot;
+  const float* inv_freq;
+  const int32_t* row_seq;
+  const int32_t* row_pos;
+  const int32_t* page_off;
+  const int32_t* page_ids;
+  int page_size;
+  void* cache;                 /* bfloat16 pages of the schedule entry; null: queries only */
+  void* q_out;                 /* bfloat16 [rows, n_q_heads, hd] */
+} SbRopeStore;
+
+/* What may accompany a product (all optional): the RMSNorm of its finished rows, memory to ask
+ * into L2 for a later kernel, and the rotation + cache write of a q|k|v product's rows (then the
+ * product's own output is not written: `out` may be null). */
 typedef struct SbLinearExtras {
   const void* norm_weight;     /* null: no norm */
   int norm_weight_dtype;
@@ -57,6 +72,7 @@ typedef struct SbLinearExtras {
   int norm_out_dtype;
   const void* warm;            /* null: nothing; else bytes a later kernel will stream */
   size_t warm_bytes;
+  const SbRopeStore* rope;     /* null: none; only where sb_gemm_tc5_fuses_rope says so */
 } SbLinearExtras;
 
 /* One row's sampling record (sb_sample reads an array of them from device memory). */
@@ -112,6 +128,10 @@ int sb_gemm_tc5_ex(const void* A, int a_dtype, const void* W, int w_dtype, int M
                    int form, const SbLinearExtras* extras, sb_stream_t stream);
 size_t sb_gemm_tc5_scratch_bytes(int M, int N, int K, int n_sms);
 int sb_gemm_tc5_fuses_norm(int M, int N, int K, int n_sms, int epilogue, int out_dtype, int form);
+/* Whether sb_gemm_tc5_ex can finish a q|k|v product of these sizes with the rotation and the
+ * cache write (the split-K decode form, bfloat16 queries and cache, head sizes in steps of 8). */
+int sb_gemm_tc5_fuses_rope(int M, int N, int K, int n_sms, int n_q_heads, int n_kv_heads, int hd,
+                           int rot, int has_kv);
 int sb_tc5_status(void);      /* 0, or the code of a bounded wait that gave up; clears it */
 
 /* Plain attention over the paged cache (float32 arithmetic, any head size up to 256). */

@@ -225,12 +225,61 @@ def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = 
     return out
 
 
+class RopeStore(ctypes.Structure):
+    """SbRopeStore of the kernel library: the rotation + cache write that finishes a q|k|v product."""
+    _fields_ = [("n_q_heads", ctypes.c_int), ("n_kv_heads", ctypes.c_int), ("hd", ctypes.c_int),
+                ("rot", ctypes.c_int), ("inv_freq", ctypes.c_void_p), ("row_seq", ctypes.c_void_p),
+                ("row_pos", ctypes.c_void_p), ("page_off", ctypes.c_void_p), ("page_ids", ctypes.c_void_p),
+                ("page_size", ctypes.c_int), ("cache", ctypes.c_void_p), ("q_out", ctypes.c_void_p)]
+
+
 class LinearExtras(ctypes.Structure):
     """SbLinearExtras of the kernel library: what may accompany a product."""
     _fields_ = [("norm_weight", ctypes.c_void_p), ("norm_weight_dtype", ctypes.c_int),
                 ("norm_eps", ctypes.c_float), ("norm_out", ctypes.c_void_p),
                 ("norm_out_dtype", ctypes.c_int), ("warm", ctypes.c_void_p),
-                ("warm_bytes", ctypes.c_size_t)]
+                ("warm_bytes", ctypes.c_size_t), ("rope", ctypes.POINTER(RopeStore))]
+
+
+def qkv_rope_store(h: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, n_q_heads: int,
+                   n_kv_heads: int, head_dim: int, rotary_dim: int, inv_freq: torch.Tensor, row_seq,
+                   row_pos, page_off, page_ids, page_size: int, cache: torch.Tensor | None,
+                   q_out: torch.Tensor) -> torch.Tensor:
+    """The fused [q | k | v] projection of the rows `h` (+ bias), the rotation of q and k, q into
+    `q_out` [rows, heads, hd] and k, v into the cache pages (`cache=None`: the weight holds the
+    query rows only).  Where the split-K decode form of the tcgen05 product runs (9 to 64 rows of
+    bfloat16), its reduce kernel does the rotation and the cache write too and the float32 row
+    is never written; else the product and `rope_store` run one after the other."""
+    M, K = h.shape
+    N = w.shape[0]
+    has_kv = cache is not None
+    l = lib()
+    fused = (h.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and q_out.dtype == torch.bfloat16
+             and (not has_kv or cache.dtype == torch.bfloat16) and K % 8 == 0
+             and (bias is None or bias.numel() == N)
+             and _pick_kernel(M, N, K, h.device) == "tc5"
+             and bool(l.sb_gemm_tc5_fuses_rope(M, N, K, _sm_count(h.device), n_q_heads, n_kv_heads, head_dim,
+                                              rotary_dim, 1 if has_kv else 0)))
+    if not fused:
+        qkv = torch.empty((M, N), dtype=torch.float32, device=h.device)
+        linear(h, w, qkv, EPI_BIAS if bias is not None else EPI_NONE, bias=bias)
+        return rope_store(qkv, n_q_heads, n_kv_heads, head_dim, rotary_dim, inv_freq, row_seq, row_pos,
+                          page_off, page_ids, page_size, cache, q_out)
+    assert inv_freq.dtype == torch.float32 and inv_freq.numel() >= rotary_dim // 2
+    rope = RopeStore(n_q_heads, n_kv_heads, head_dim, rotary_dim, inv_freq.data_ptr(),
+                     _i32(row_seq, "row_seq").value, _i32(row_pos, "row_pos").value,
+                     _i32(page_off, "page_off").value if has_kv else None,
+                     _i32(page_ids, "page_ids").value if has_kv else None, page_size,
+                     cache.data_ptr() if has_kv else None, _ptr(q_out).value)
+    extras = LinearExtras()
+    extras.rope = ctypes.pointer(rope)
+    ws = _tc5_workspace(M, N, K, h.device)
+    _check(l.sb_gemm_tc5_ex(_ptr(h), BF16, _ptr(w), BF16, M, N, K, EPI_BIAS if bias is not None else EPI_NONE,
+                            _ptr(bias), _code(bias.dtype) if bias is not None else 0, _ptr(None), _ptr(None), F32,
+                            _ptr(ws), ctypes.c_size_t(ws.numel()), _sm_count(h.device), 0,
+                            ctypes.byref(extras), _stream()),
+           "q|k|v product with rotation (tcgen05 kernel)", launches=2)
+    return q_out
 
 
 def _warm_args(warm):

@@ -64,16 +64,14 @@ class Attention(Mixer):
         rows = h.shape[0]
         plan = ctx.plan
         width_in = self.qw + (2 * self.kvw if ctx.owns_cache else 0)
-        qkv = torch.empty((rows, width_in), dtype=torch.float32, device=h.device)
-        ops.linear(h, self.w_qkv[:width_in], qkv,
-                   ops.EPI_BIAS if self.b_qkv is not None else ops.EPI_NONE,
-                   bias=self.b_qkv[:width_in] if self.b_qkv is not None else None)
         storage = ctx.kv_storage()
         g = plan.groups[ctx.kv_group()]
         q = torch.empty((rows, self.hq, self.hd), dtype=self.dtype, device=h.device)
-        ops.rope_store(qkv, self.hq, self.hkv, self.hd, self.position.rotary_dim,
-                       self.position.inv_freq, plan.row_seq, plan.row_pos, g.page_off, g.page_ids,
-                       g.page_size, storage if ctx.owns_cache else None, q)
+        ops.qkv_rope_store(h, self.w_qkv[:width_in],
+                           self.b_qkv[:width_in] if self.b_qkv is not None else None, self.hq, self.hkv,
+                           self.hd, self.position.rotary_dim, self.position.inv_freq, plan.row_seq,
+                           plan.row_pos, g.page_off, g.page_ids, g.page_size,
+                           storage if ctx.owns_cache else None, q)
         mixed = torch.empty((rows, self.qw), dtype=self.dtype, device=h.device)
         ops.attention(q, mixed, plan, ctx.kv_group(), storage, self.hq, self.hkv, self.hd,
                       self.spec.window, self.spec.scale, warm=self.w_o)

@@ -586,6 +586,56 @@ def test_sampled_tokens_do_not_depend_on_the_row():
     assert a == b[::-1]
 
 
+@pytest.mark.parametrize("hq,hkv,hd,K,rot", [(28, 4, 128, 3584, 128), (6, 2, 64, 192, 64), (8, 2, 64, 2048, 32),
+                                             (4, 4, 128, 1024, 0)])
+@pytest.mark.parametrize("rows", [3, 9, 33, 64, 70])
+def test_fused_projection_rotation_and_cache_write(hq, hkv, hd, K, rot, rows):
+    """`qkv_rope_store` (where the split-K product's reduce kernel also rotates and writes the
+    cache: 9 to 64 rows of the larger sizes) against the product and `rope_store` one after the
+    other: the same queries and the same cache pages, for rows of several sequences at unequal
+    positions, with a partly rotated head, without rotation, and for queries only."""
+    dt = torch.bfloat16
+    N = (hq + 2 * hkv) * hd
+    a, w = rnd(rows, K, dtype=dt), rnd(N, K, dtype=dt, scale=K ** -0.5, seed=1)
+    bias = rnd(N, dtype=dt, seed=2)
+    inv = torch.from_numpy(np.exp(-2.0 * np.arange(max(rot // 2, 1), dtype=np.float32) / np.float32(max(rot, 1))
+                                  * np.log(np.float32(10000.0))).astype(np.float32)).to(DEV)
+    lens = [rows - 2 * (rows // 3), rows // 3, rows // 3] if rows >= 3 else [rows]
+    results = []
+    for fused in (True, False):
+        cache = make_cache(hkv, hd, 0, dt, max_tokens=64 * 8)
+        slots = [cache.open() for _ in lens]
+        for i, (s, n) in enumerate(zip(slots, lens)):      # unequal starting positions
+            cache.reserve(s, 37 * i + n)
+            cache.advance(s, 37 * i)
+        plan = StepPlan(cache, [StepEntry(s, [0] * n, []) for s, n in zip(slots, lens)], DEV)
+        g = plan.groups[0]
+        storage = cache.groups[0].entry_storage(0)
+        q = torch.empty(rows, hq, hd, dtype=dt, device=DEV)
+        if fused:
+            ops.qkv_rope_store(a, w, bias, hq, hkv, hd, rot, inv, plan.row_seq, plan.row_pos, g.page_off,
+                               g.page_ids, g.page_size, storage, q)
+        else:
+            qkv = torch.empty(rows, N, device=DEV)
+            ops.linear(a, w, qkv, ops.EPI_BIAS, bias=bias)
+            ops.rope_store(qkv, hq, hkv, hd, rot, inv, plan.row_seq, plan.row_pos, g.page_off, g.page_ids,
+                           g.page_size, storage, q)
+        results.append((q.float().cpu(), storage.float().cpu()))
+    (q1, c1), (q2, c2) = results
+    assert float(c2.abs().max()) > 0
+    assert pm.rel_err(q1, q2) < 4e-3 and pm.rel_err(c1, c2) < 4e-3       # an ulp of bfloat16 at most
+    # queries only (a layer that reads another layer's cache)
+    qa, qb = torch.empty(rows, hq, hd, dtype=dt, device=DEV), torch.empty(rows, hq, hd, dtype=dt, device=DEV)
+    plan = StepPlan(cache, [StepEntry(s, [0] * n, []) for s, n in zip(slots, lens)], DEV)
+    ops.qkv_rope_store(a, w[:hq * hd], bias[:hq * hd], hq, hkv, hd, rot, inv, plan.row_seq, plan.row_pos, None,
+                       None, 64, None, qa)
+    qkv = torch.empty(rows, hq * hd, device=DEV)
+    ops.linear(a, w[:hq * hd].contiguous(), qkv, ops.EPI_BIAS, bias=bias[:hq * hd].contiguous())
+    ops.rope_store(qkv, hq, hkv, hd, rot, inv, plan.row_seq, plan.row_pos, None, None, 64, None, qb)
+    assert pm.rel_err(qa.float().cpu(), qb.float().cpu()) < 4e-3
+    assert ops.tc5_status() == 0
+
+
 # ------------------------------------------------ positions outside a sequence's own pages
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("hq,hkv,hd,rows", [(4, 2, 16, 3), (28, 4, 128, 3), (4, 2, 16, 80), (8, 4, 64, 60)])
