@@ -472,7 +472,7 @@ tc5_reduce_kernel(const Tc5Params p, int bn) {
 // token and a share of its heads; a task is four pairs (e, e + half) of one head, or four of the
 // values beyond the rotated part.  cos and sin of the token's position are worked out once a
 // block (from the step's plan, before the wait for the product).
-constexpr int RR_THREADS = 256, RR_HEAD_SHARES = 4;
+constexpr int RR_THREADS = 256;
 __global__ void __launch_bounds__(RR_THREADS)
 tc5_reduce_rope_kernel(const Tc5Params p, int bn, const SbRopeStore r) {
   extern __shared__ float rr_cs[];                   // cos[rot/2], then sin[rot/2]
@@ -501,7 +501,7 @@ tc5_reduce_rope_kernel(const Tc5Params p, int bn, const SbRopeStore r) {
   __syncthreads();
   sb_pdl_wait();
   const int pair_tasks = half >> 2, per_head = pair_tasks + ((hd - r.rot) >> 2);
-  const int heads_per = (n_heads + RR_HEAD_SHARES - 1) / RR_HEAD_SHARES;
+  const int heads_per = (n_heads + (int)gridDim.y - 1) / (int)gridDim.y;
   const int head_lo = blockIdx.y * heads_per, head_hi = min(n_heads, head_lo + heads_per);
   bf16* q_out = (bf16*)r.q_out;
   bf16* cache = (bf16*)r.cache;
@@ -917,7 +917,11 @@ static int tc5_run(const void* A, int a_dtype, const void* W, int w_dtype, int M
   if (rc != SB_OK || splits <= 1) return rc;
   if (rope) {
     const size_t smem = (size_t)(rope->rot > 0 ? rope->rot : 2) * sizeof(float);
-    sb_launch<SB_K_REDUCE>(tc5_reduce_rope_kernel, dim3((unsigned)M, RR_HEAD_SHARES), dim3(RR_THREADS), smem,
+    // the heads of a token are shared out over enough blocks for two per SM, at least four
+    const int n_heads = rope->n_q_heads + (rope->cache ? 2 * rope->n_kv_heads : 0);
+    int shares = n_sms > 0 ? (2 * n_sms + M - 1) / M : 4;
+    shares = shares < 4 ? 4 : (shares > n_heads ? n_heads : shares);
+    sb_launch<SB_K_REDUCE>(tc5_reduce_rope_kernel, dim3((unsigned)M, (unsigned)shares), dim3(RR_THREADS), smem,
                            stream, p, bn, *rope);
     SB_CHECK_LAUNCH("sb_gemm_tc5 (reduce + rotation)");
     return SB_OK;

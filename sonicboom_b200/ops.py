@@ -290,7 +290,8 @@ def _warm_args(warm):
 
 
 WARM = _os.environ.get("SB_WARM", "1") != "0"       # L2 hints on (SB_WARM=0: off, for measurements)
-FORCE_DECODE_KERNEL = None      # "skinny" or "tc5": overrides the choice below (for measurements)
+# "skinny" or "tc5": overrides the choice below (for measurements; SB_DECODE_KERNEL in the environment)
+FORCE_DECODE_KERNEL = _os.environ.get("SB_DECODE_KERNEL") or None
 
 
 def _pick_kernel(M: int, N: int, K: int, device) -> str:
