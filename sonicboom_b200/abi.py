@@ -27,6 +27,7 @@ CORE = {
     "sb_embed": ("i", "pipiiifps"),
     "sb_rmsnorm": ("i", "ppiipifpis"),
     "sb_softcap": ("i", "pzfs"),
+    "sb_add_bias": ("i", "ppiiis"),
     "sb_cast": ("i", "pipizs"),
     "sb_rope_store": ("i", "piiiiipppppipipiis"),
     "sb_gemm_plain": ("i", _GEMM),

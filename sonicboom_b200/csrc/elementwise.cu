@@ -205,6 +205,33 @@ extern "C" int sb_softcap(float* x, size_t n, float cap, cudaStream_t stream) {
   return SB_OK;
 }
 
+// -------------------------------------------------------------------------------- row bias
+// x[m, n] += bias[n] in place on float32 rows: the bias of a projection whose product epilogue is
+// taken by the residual add (an output projection with a bias; the reference keeps such a bias
+// as its own AddBias node, core/src/model/emit.cpp:203-210).
+template <typename TB>
+__global__ void add_bias_kernel(float* x, const TB* __restrict__ bias, size_t rows, int width) {
+  sb_pdl_launch();
+  sb_pdl_wait();
+  const size_t n = rows * (size_t)width;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    x[i] += sb_to_f32<TB>(bias[i % width]);
+}
+
+extern "C" int sb_add_bias(float* x, const void* bias, int bias_dtype, int rows, int width,
+                           cudaStream_t stream) {
+  if (rows <= 0 || width <= 0 || !x || !bias) SB_FAIL(SB_ERR_ARG, "sb_add_bias: rows=%d width=%d", rows, width);
+  if (!sb_valid_dtype(bias_dtype)) SB_FAIL(SB_ERR_ARG, "sb_add_bias: dtype code %d", bias_dtype);
+  const size_t n = (size_t)rows * width;
+  const int blocks = (int)((n + 255) / 256 < 4096 ? (n + 255) / 256 : 4096);
+  SB_DISPATCH_DTYPE(bias_dtype, TB, {
+    sb_launch<SB_K_ELEMENTWISE>(add_bias_kernel<TB>, dim3(blocks), dim3(256), 0, stream, x, (const TB*)bias,
+                                (size_t)rows, width);
+  });
+  SB_CHECK_LAUNCH("sb_add_bias");
+  return SB_OK;
+}
+
 // ------------------------------------------------------------------------------------ cast
 template <typename TI, typename TO>
 __global__ void cast_kernel(const TI* in, TO* out, size_t n) {

@@ -99,6 +99,7 @@ int sb_embed(const int32_t* tokens, int n_rows, const void* table, int table_dty
 int sb_rmsnorm(const float* x, const int32_t* rows, int n_rows, int width, const void* weight,
                int weight_dtype, float eps, void* out, int out_dtype, sb_stream_t stream);
 int sb_softcap(float* x, size_t n, float cap, sb_stream_t stream);     /* x = cap tanh(x / cap) */
+int sb_add_bias(float* x, const void* bias, int bias_dtype, int rows, int width, sb_stream_t stream);   /* x[m, n] += bias[n] */
 int sb_cast(const void* in, int in_dtype, void* out, int out_dtype, size_t n, sb_stream_t stream);
 /* Rotates q and k of the fused row [q | k | v], writes q to q_out and k, v into the pages of
  * each row's sequence; a position without a page in its own sequence's list writes nothing. */

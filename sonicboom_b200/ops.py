@@ -113,6 +113,14 @@ def embed(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor,
     return out
 
 
+def add_bias(x: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
+    """x[m, n] += bias[n] in place (x float32 [rows, width])."""
+    assert x.dtype == torch.float32 and x.dim() == 2 and bias.numel() == x.shape[1]
+    _check(lib().sb_add_bias(_ptr(x), _ptr(bias), _code(bias.dtype), x.shape[0], x.shape[1], _stream()),
+           "add_bias")
+    return x
+
+
 def softcap(x: torch.Tensor, cap: float) -> torch.Tensor:
     """x = cap * tanh(x / cap) in place (float32)."""
     assert x.dtype == torch.float32 and x.is_contiguous()

@@ -3,8 +3,8 @@
 Order of operations as the reference's emitter writes it (core/src/model/emit.cpp:255-308):
 q = Wq h + bq; rotate q; k = Wk h, v = Wv h, then their biases; rotate k; store k, v; attend
 with scale applied after the dot and a causal (optionally windowed) mask
-(core/src/nn/attention.cpp:26-105); output projection without bias; the residual add is
-fused into that projection.  The three input projections are one product over a fused
+(core/src/nn/attention.cpp:26-105); output projection (without bias in this architecture; a
+spec may ask for one); the residual add is fused into that projection.  The three input projections are one product over a fused
 [q | k | v] matrix, the way the reference reads "sibling" weights in one launch
 (core/src/quant/mmvq_q8_1.cuh:634).  An entry that reads another entry's cache projects
 queries only."""
@@ -24,14 +24,11 @@ class Attention(Mixer):
         self.spec, self.dtype, self.device = spec, dtype, device
         self.hq, self.hkv, self.hd = spec.n_heads, spec.n_kv_heads, spec.head_dim
         self.qw, self.kvw = self.hq * self.hd, self.hkv * self.hd
-        if spec.out_bias:
-            from ..config.specs import ConfigError
-            raise ConfigError("attention with an output-projection bias is not built")
         if self.hq % self.hkv:
             from ..config.specs import ConfigError
             raise ConfigError(f"{self.hq} query heads are not a multiple of {self.hkv} key/value heads")
         self.position = make(POSITION_ENCODINGS, "position encoding", spec.position, dtype, device)
-        self.w_qkv = self.b_qkv = self.w_o = None
+        self.w_qkv = self.b_qkv = self.w_o = self.b_o = None
 
     def kv_need(self):
         return KVNeed(self.hkv, self.hd, self.spec.window)
@@ -46,6 +43,8 @@ class Attention(Mixer):
             req += [TensorRequest(p + "q_proj.bias", (self.qw,), "bias"),
                     TensorRequest(p + "k_proj.bias", (self.kvw,), "bias"),
                     TensorRequest(p + "v_proj.bias", (self.kvw,), "bias")]
+        if self.spec.out_bias:
+            req.append(TensorRequest(p + "o_proj.bias", (d,), "bias"))
         return req
 
     def bind(self, get):
@@ -54,6 +53,8 @@ class Attention(Mixer):
         if self.spec.qkv_bias:
             self.b_qkv = _cat([get(p + f"{n}_proj.bias") for n in "qkv"])
         self.w_o = get(p + "o_proj.weight")
+        if self.spec.out_bias:
+            self.b_o = get(p + "o_proj.bias")
 
     def first_weights(self, rows):
         n, k = self.w_qkv.shape
@@ -77,9 +78,13 @@ class Attention(Mixer):
                       self.spec.window, self.spec.scale, warm=self.w_o)
         out = residual if residual is not None else \
             torch.empty((rows, self.spec.width), dtype=torch.float32, device=h.device)
-        return ctx.linear(mixed, self.w_o, out,
-                          ops.EPI_RESIDUAL if residual is not None else ops.EPI_NONE,
-                          residual=residual, act_dtype=self.dtype)
+        epilogue = ops.EPI_RESIDUAL if residual is not None else ops.EPI_NONE
+        if self.b_o is None:
+            return ctx.linear(mixed, self.w_o, out, epilogue, residual=residual, act_dtype=self.dtype)
+        # with an output bias (not this architecture's): the bias follows the product as a step
+        # of its own, so no norm rides on the product
+        ops.linear(mixed, self.w_o, out, epilogue, residual=residual)
+        return ops.add_bias(out, self.b_o)
 
 
 def _cat(tensors):

@@ -74,6 +74,16 @@ def test_norm_mixer_feed_forward_and_block_alone(oracles, name, dtype):
     ctx2 = ctx_for([mixer.kv_need()], lens, dt)
     with_res = mixer.forward(hin, ctx2, residual=res.clone()).cpu()
     assert pm.rel_err(with_res, mixed + res.cpu()) < tol
+    # an output-projection bias (not this architecture's, but a spec may ask for one)
+    biased_spec = dataclasses.replace(layer.mixer, out_bias=True)
+    o_bias = torch.randn(spec.width, generator=torch.Generator().manual_seed(3)) * 0.1
+    biased = bound(parts.make(parts.MIXERS, "mixer", biased_spec, dt, DEV),
+                   dict(tensors, **{layer.mixer.prefix + "o_proj.bias": o_bias}), dt)
+    assert any(r.name.endswith("o_proj.bias") for r in biased.tensor_requests())
+    ctx4 = ctx_for([mixer.kv_need()], lens, dt)
+    with_bias = biased.forward(hin, ctx4, residual=res.clone()).cpu()
+    expect = with_res + (o_bias.to(dt).float() if dtype == "bfloat16" else o_bias)
+    assert pm.rel_err(with_bias, expect) < (1e-6 if dtype == "float32" else 1e-5)
 
     ffn = bound(parts.make(parts.FEED_FORWARDS, "feed-forward", layer.feed_forward, dt, DEV), tensors, dt)
     p = f"model.layers.{li}.mlp."
