@@ -39,6 +39,7 @@ CORE = {
     "sb_gemm_tc5_fuses_norm": ("i", "iiiiiii"),
     "sb_gemm_tc5_fuses_rope": ("i", "iiiiiiiii"),
     "sb_tc5_status": ("i", ""),
+    "sb_gemm_tc5_pairs": ("v", "i"),
     "sb_attention_plain": ("i", "ppiippppipiiiiifs"),
     "sb_sample_params_size": ("i", ""),
     "sb_sample": ("i", "piippipps"),

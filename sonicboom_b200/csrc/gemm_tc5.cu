@@ -425,6 +425,12 @@ gemm_tc5_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
   if (warp == 1) tmem_dealloc(tmem_base, 512);
 }
 
+}  // namespace
+
+#include "gemm_tc5_pair.cuh"
+
+namespace {
+
 // Adds the partial tiles of a split-K swapped product in split order and applies the epilogue.
 // One thread takes four consecutive features of one token (for the fused gate/up: four gates and
 // their four up values).  A second, fully parallel kernel measured faster here than letting the
@@ -740,12 +746,73 @@ int persistent_bn(int M, int N, int n_sms) {
   return best;
 }
 
+// The pair kernel: clusters of two blocks, as many as the device runs at once (cached per kernel).
+template <int BN, typename TO>
+int pair_clusters() {
+  static int clusters = -1;
+  if (clusters >= 0) return clusters;
+  constexpr int smem = pair_smem_bytes(BN, PAIR_STAGES);
+  clusters = 0;
+  if (cudaFuncSetAttribute(gemm_tc5_pair_kernel<BN, PAIR_STAGES, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           smem) != cudaSuccess) {
+    cudaGetLastError();
+    return clusters;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2);
+  cfg.blockDim = dim3(THREADS);
+  cfg.dynamicSmemBytes = smem;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, gemm_tc5_pair_kernel<BN, PAIR_STAGES, TO>, &cfg) == cudaSuccess && n > 0)
+    clusters = n;
+  else
+    cudaGetLastError();
+  return clusters;
+}
+
+template <int BN, typename TO>
+int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const Tc5Params& p, int clusters,
+                cudaStream_t stream) {
+  sb_launch<SB_K_TC5>(gemm_tc5_pair_kernel<BN, PAIR_STAGES, TO>, dim3(2 * clusters), dim3(THREADS),
+                      pair_smem_bytes(BN, PAIR_STAGES), stream, ma, mb, p);
+  SB_CHECK_LAUNCH("sb_gemm_tc5 (pairs)");
+  return SB_OK;
+}
+
+// Whether products of more than 128 rows run on pairs of SMs: sb_gemm_tc5_pairs(0 or 1) decides,
+// else the environment (SB_TC5_PAIR=0 keeps every product on the one-block kernels).
+int g_pair_mode = -1;
+bool pair_enabled() {
+  if (g_pair_mode >= 0) return g_pair_mode != 0;
+  static const bool on = [] {
+    const char* e = getenv("SB_TC5_PAIR");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
+
+// Tile width of the pair kernel: as persistent_bn, with 256-row tiles over clusters of two.
+int pair_bn(int M, int N, int clusters) {
+  const int tiles_m = (M + PAIR_M - 1) / PAIR_M;
+  int best = 0;
+  long best_cost = 0;
+  for (int bn : PERSIST_BNS) {
+    const long tiles = (long)tiles_m * ((N + bn - 1) / bn);
+    const long cost = ((tiles + clusters - 1) / clusters) * bn;
+    if (!best || cost < best_cost) { best = bn; best_cost = cost; }
+  }
+  return best;
+}
+
 }  // namespace
 
 // 0 when no kernel has given up on a wait since the last call; else the code of the wait
 // (1 producer/empty, 2 producer drain, 3 MMA/full, 4 epilogue/accumulator).  Reading
 // synchronizes with the device.
 extern "C" int sb_tc5_status() { return tc5_read_status(); }
+
+// 1: products of more than 128 rows run on pairs of SMs, 0: on single SMs, -1: by the environment.
+extern "C" void sb_gemm_tc5_pairs(int mode) { g_pair_mode = mode; }
 
 namespace {
 
@@ -857,6 +924,32 @@ static int tc5_run(const void* A, int a_dtype, const void* W, int w_dtype, int M
   // form: 0 picks by the number of rows, 1 forces the normal form, 2 the swapped form
   const bool normal = form == 1 || (form == 0 && M > 64);
   if (form == 2 && M > 64) SB_FAIL(SB_ERR_UNSUPPORTED, "sb_gemm_tc5: the swapped form takes at most 64 rows");
+  if (normal && N >= 192 && n_sms > 1 && M > BM && pair_enabled()) {
+    // at least two row tiles, wide output: the persistent kernel on pairs of SMs
+    const int bn = pair_bn(M, N, n_sms / 2);
+    p.tiles_a = (M + PAIR_M - 1) / PAIR_M;
+    p.tiles_b = (N + bn - 1) / bn;
+    const long n_tiles = (long)p.tiles_a * p.tiles_b;
+    if (n_tiles > 2147483647L) SB_FAIL(SB_ERR_UNSUPPORTED, "sb_gemm_tc5: too many tiles");
+    int clusters = 0;
+#define SB_TC5_PAIR_CLUSTERS(BN_)                                                                  \
+    if (bn == BN_) clusters = out_dtype == SB_F32 ? pair_clusters<BN_, float>() : pair_clusters<BN_, bf16>();
+    SB_TC5_PAIR_CLUSTERS(256) SB_TC5_PAIR_CLUSTERS(240) SB_TC5_PAIR_CLUSTERS(224) SB_TC5_PAIR_CLUSTERS(208)
+    SB_TC5_PAIR_CLUSTERS(192)
+#undef SB_TC5_PAIR_CLUSTERS
+    if (clusters > 0) {                               // else: the one-block kernel below
+      if (!make_map(&ma, A, M, K, BM) || !make_map(&mb, W, N, K, bn / 2))
+        SB_FAIL(SB_ERR_CUDA, "sb_gemm_tc5: cuTensorMapEncodeTiled failed");
+      if (n_tiles < clusters) clusters = (int)n_tiles;
+#define SB_TC5_PAIR_LAUNCH(BN_)                                                                    \
+      if (bn == BN_)                                                                               \
+        return out_dtype == SB_F32 ? launch_pair<BN_, float>(ma, mb, p, clusters, stream)          \
+                                   : launch_pair<BN_, bf16>(ma, mb, p, clusters, stream);
+      SB_TC5_PAIR_LAUNCH(256) SB_TC5_PAIR_LAUNCH(240) SB_TC5_PAIR_LAUNCH(224) SB_TC5_PAIR_LAUNCH(208)
+      SB_TC5_PAIR_LAUNCH(192)
+#undef SB_TC5_PAIR_LAUNCH
+    }
+  }
   if (normal && N >= 192 && n_sms > 0) {
     // many rows, wide output: the persistent kernel
     const int bn = persistent_bn(M, N, n_sms);

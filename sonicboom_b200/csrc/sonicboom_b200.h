@@ -134,6 +134,7 @@ int sb_gemm_tc5_fuses_norm(int M, int N, int K, int n_sms, int epilogue, int out
 int sb_gemm_tc5_fuses_rope(int M, int N, int K, int n_sms, int n_q_heads, int n_kv_heads, int hd,
                            int rot, int has_kv);
 int sb_tc5_status(void);      /* 0, or the code of a bounded wait that gave up; clears it */
+void sb_gemm_tc5_pairs(int mode);   /* products of more than 128 rows on pairs of SMs: 1 yes, 0 no, -1 by SB_TC5_PAIR */
 
 /* Plain attention over the paged cache (float32 arithmetic, any head size up to 256). */
 int sb_attention_plain(const void* q, void* out, int act_dtype, int n_rows, const int32_t* row_seq,

@@ -374,6 +374,13 @@ def tc5_status() -> int:
     return int(lib().sb_tc5_status())
 
 
+def set_tc5_pairs(mode: int) -> None:
+    """Whether the tcgen05 product of more than 128 rows runs on pairs of SMs (a cluster of two
+    blocks on one 256-row tile): 1 yes, 0 no (one block per 128-row tile), -1 by SB_TC5_PAIR
+    (default yes).  The result is the same to the bit either way."""
+    lib().sb_gemm_tc5_pairs(int(mode))
+
+
 def rope_store(qkv: torch.Tensor, n_q_heads: int, n_kv_heads: int, head_dim: int, rotary_dim: int,
                inv_freq: torch.Tensor, row_seq, row_pos, page_off, page_ids, page_size: int,
                cache: torch.Tensor | None, q_out: torch.Tensor) -> torch.Tensor:

@@ -123,23 +123,54 @@ def test_linear_epilogues(M, N, K, dtype, kernel):
     assert ops.tc5_status() == 0
 
 
-@pytest.mark.parametrize("M,N,K", [(1280, 3568, 72), (1280, 3344, 72), (1280, 3120, 72), (2048, 3568, 136),
-                                   (200, 528, 328)])
-def test_persistent_product_at_every_tile_width(M, N, K):
-    """Sizes for which the persistent tcgen05 product picks each of its tile widths on 148 SMs
-    (256, 240, 224, 208, 192), with a last tile that is only partly inside the matrix: every
-    epilogue against the float64 product.  Widths that are odd multiples of 16 end in a chunk
-    of 16 columns."""
+def _every_epilogue(M, N, K):
     dt = torch.bfloat16
     a, w = rnd(M, K, dtype=dt), rnd(N, K, dtype=dt, scale=K ** -0.5, seed=1)
     bias, res = rnd(N, dtype=dt, seed=2), rnd(M, N, seed=3)
+    outs = []
     for epi, odt in [(ops.EPI_NONE, torch.float32), (ops.EPI_BIAS, dt), (ops.EPI_RESIDUAL, torch.float32),
                      (ops.EPI_SWIGLU, dt)]:
         out = torch.empty(M, N // 2 if epi == ops.EPI_SWIGLU else N, dtype=odt, device=DEV)
         ops.linear(a, w, out, epi, bias=bias if epi == ops.EPI_BIAS else None,
                    residual=res.clone() if epi == ops.EPI_RESIDUAL else None, kernel="tc5")
         close(out, linear_ref(a, w, epi, bias, res), 1e-5 if odt == torch.float32 else 5e-3)
+        outs.append(out)
     assert ops.tc5_status() == 0
+    return outs
+
+
+@pytest.mark.parametrize("M,N,K", [(1280, 3568, 72), (1280, 3344, 72), (1280, 3120, 72), (2048, 3568, 136),
+                                   (200, 528, 328)])
+def test_persistent_product_at_every_tile_width(M, N, K):
+    """Sizes for which the persistent tcgen05 product with one block per tile picks each of its
+    tile widths on 148 SMs (256, 240, 224, 208, 192), with a last tile that is only partly inside
+    the matrix: every epilogue against the float64 product.  Widths that are odd multiples of 16
+    end in a chunk of 16 columns."""
+    ops.set_tc5_pairs(0)
+    try:
+        _every_epilogue(M, N, K)
+    finally:
+        ops.set_tc5_pairs(-1)
+
+
+@pytest.mark.parametrize("M,N,K", [(1280, 3376, 72), (1280, 3152, 72), (1280, 2928, 72), (1280, 2720, 136),
+                                   (300, 400, 328), (129, 528, 64), (2048, 4608, 1032)])
+def test_product_on_pairs_of_sms(M, N, K):
+    """The same product on clusters of two blocks (one MMA of 256 rows over two SMs), at sizes for
+    which it picks each tile width on 74 pairs (256, 240, 224, 208, 192; the last two sizes 256):
+    rows that end inside the first block's half of a tile (129), inside the second's (300: the
+    second tile's second block loads nothing but zeros), last tiles partly outside, several K
+    tiles per stage of the ring (1,032 = 17 tiles, the last one of 8 values).  Every epilogue
+    against the float64 product, and the same bits as one block per tile gives."""
+    ops.set_tc5_pairs(1)
+    try:
+        pairs = _every_epilogue(M, N, K)
+        ops.set_tc5_pairs(0)
+        single = _every_epilogue(M, N, K)
+    finally:
+        ops.set_tc5_pairs(-1)
+    for a, b in zip(pairs, single):
+        assert torch.equal(a, b)
 
 
 @pytest.mark.parametrize("kernel", ["plain", "skinny", "tiled", "tc5"])
