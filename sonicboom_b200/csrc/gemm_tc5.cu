@@ -34,6 +34,12 @@ typedef __nv_bfloat16 bf16;
 
 constexpr int BM = 128, BK = 64, UMMA_K = 16;
 constexpr int THREADS = 192;
+// The decode form with 64 tokens has two groups of four epilogue warps: a warp reaches only its
+// own quarter of the tensor memory's lanes (weight rows), so the second group takes the second
+// half of the columns (tokens).  With one group the epilogue of the last wave of blocks, beside
+// which nothing else runs, took 5 of the fused gate/up product's 46 microseconds.
+constexpr int epilogue_groups(int bn, bool swapped) { return swapped && bn == 64 ? 2 : 1; }
+constexpr int kernel_threads(int bn, bool swapped) { return 64 + 128 * epilogue_groups(bn, swapped); }
 // Shared-memory matrix descriptor of a K-major tile with the 128-byte swizzle: rows of 128
 // bytes, groups of 8 rows 1024 bytes apart.
 __device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
@@ -43,6 +49,15 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
 // Instruction descriptor: float32 accumulator, bfloat16 A and B, both K-major, M = 128, N = bn.
 __host__ __device__ constexpr uint32_t instr_desc(int bn) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+// SiLU of a value that is rounded to TO afterwards: for bfloat16 outputs with the hardware's
+// exponential (relative error about 1e-6 against bfloat16's 4e-3; a gate so negative that the
+// exponential overflows gives 1 / inf = 0, as it should); for float32 outputs the accurate one.
+template <typename TO>
+__device__ __forceinline__ float sb_silu_out(float x) {
+  if (sizeof(TO) == 2) return x * __frcp_rn(1.0f + __expf(-x));
+  return sb_silu(x);
 }
 
 template <typename TB>
@@ -86,7 +101,7 @@ __device__ __forceinline__ void store_chunk(const Tc5Params& p, float* stage, co
       const int row = rr + (lane >> 4), m = m_base + row;
       if (m < p.M && live)
         ((TO*)p.out)[(size_t)m * (p.N / 2) + n0 / 2 + o] =
-            sb_from_f32<TO>(sb_silu(stage[row * 33 + src]) * stage[row * 33 + src + 8]);
+            sb_from_f32<TO>(sb_silu_out<TO>(stage[row * 33 + src]) * stage[row * 33 + src + 8]);
     }
     return;
   }
@@ -121,7 +136,7 @@ __device__ __forceinline__ void store_chunk(const Tc5Params& p, float* stage, co
 // SWAPPED = false: A rows are tokens (m), B rows are features (n).
 // SWAPPED = true:  A rows are features (n), B rows are tokens (m <= BN).
 template <int BN, int STAGES, bool SWAPPED, typename TO>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(kernel_threads(BN, SWAPPED))
 gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                 const Tc5Params p) {
   extern __shared__ unsigned char smem_raw[];
@@ -241,40 +256,58 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           store_chunk<TO>(p, stage, r, m_base, n0, lane);
         }
       } else {
-        // swapped: this thread owns feature n = a_row and holds its value for every token
+        // swapped: this thread owns feature n = a_row and holds its value for the CN tokens
+        // from t0 on (all BN of them unless the epilogue warps come in two groups)
+        constexpr int CN = BN / epilogue_groups(BN, SWAPPED);
+        const int t0 = ((warp - 2) >> 2) * CN;
         const int n = a_row;
         uint32_t r[32];
-        float acc[BN];
+        float acc[CN];
 #pragma unroll
-        for (int c = 0; c < (BN + 31) / 32; ++c) {
-          if (BN >= 32) tmem_ld32(t_row + c * 32, r); else tmem_ld16(t_row, r);
+        for (int c = 0; c < (CN + 31) / 32; ++c) {
+          if (CN >= 32) tmem_ld32(t_row + t0 + c * 32, r); else tmem_ld16(t_row + t0, r);
 #pragma unroll
-          for (int j = 0; j < (BN < 32 ? BN : 32); ++j) acc[c * 32 + j] = __uint_as_float(r[j]);
+          for (int j = 0; j < (CN < 32 ? CN : 32); ++j) acc[c * 32 + j] = __uint_as_float(r[j]);
         }
         if (p.k_splits > 1) {
           // partial tile to scratch: [tile][split][token][128 features]
-          float* dst = p.scratch + (((size_t)tile_a * p.k_splits + split) * BN) * BM + q * 32 + lane;
+          float* dst = p.scratch + (((size_t)tile_a * p.k_splits + split) * BN + t0) * BM + q * 32 + lane;
 #pragma unroll
-          for (int j = 0; j < BN; ++j)
-            if (j < p.M) dst[(size_t)j * BM] = acc[j];
+          for (int j = 0; j < CN; ++j)
+            if (t0 + j < p.M) dst[(size_t)j * BM] = acc[j];
+        } else if (p.epilogue == SB_EPI_SWIGLU) {
+          // Features come in groups of 8 gates then their 8 up values, so lane l of a gate
+          // group and lane l + 8 hold the two factors of one output.  They take a token each
+          // of every two: the gate lane hands over its gate of the odd token and gets the up
+          // value of the even one, so that every lane computes and stores one output per
+          // exchange.  Nothing leaves the loop early: tokens beyond M are zero rows whose
+          // results are not stored, and without branches the exchanges, exponentials and
+          // divisions of different tokens overlap (with 64 tokens the epilogue of the last wave
+          // of blocks was a chain of their latencies, and nothing else runs beside it).
+          const bool gate = (lane & 15) < 8;
+          const int col = (n >> 4) * 8 + (n & 7);               // the same for both lanes of an output
+          const bool live = n < p.N;                            // N is a multiple of 16 here
+#pragma unroll
+          for (int j = 0; j < CN; j += 2) {
+            const float a0 = acc[j], a1 = acc[j + 1];
+            const float other = __shfl_xor_sync(0xffffffffu, gate ? a1 : a0, 8);
+            const int tok = t0 + (gate ? j : j + 1);
+            const float g = gate ? a0 : other, up = gate ? other : a1;
+            if (live && tok < p.M)
+              ((TO*)p.out)[(size_t)tok * (p.N / 2) + col] = sb_from_f32<TO>(sb_silu_out<TO>(g) * up);
+          }
         } else {
 #pragma unroll
-          for (int j = 0; j < BN; ++j) {
-            if (j >= p.M) break;
+          for (int j = 0; j < CN; ++j) {
+            const int tok = t0 + j;
+            if (tok >= p.M) break;
             float v = acc[j];
-            if (p.epilogue == SB_EPI_SWIGLU) {
-              const float up = __shfl_down_sync(0xffffffffu, v, 8);
-              if ((lane & 15) < 8 && n < p.N)
-                ((TO*)p.out)[(size_t)j * (p.N / 2) + (n >> 4) * 8 + (n & 7)] =
-                    sb_from_f32<TO>(sb_silu(v) * up);
-              continue;
-            }
             if (n >= p.N) continue;
             if (p.epilogue == SB_EPI_BIAS)
               v += p.bias_dtype == SB_F32 ? bias_at<float>(p.bias, n) : bias_at<bf16>(p.bias, n);
             else if (p.epilogue == SB_EPI_RESIDUAL)
-              v += p.residual[(size_t)j * p.N + n];
-            ((TO*)p.out)[(size_t)j * p.N + n] = sb_from_f32<TO>(v);
+              v += p.residual[(size_t)tok * p.N + n];
+            ((TO*)p.out)[(size_t)tok * p.N + n] = sb_from_f32<TO>(v);
           }
         }
       }
@@ -696,7 +729,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const Tc5Params& p, int
       SB_FAIL(SB_ERR_CUDA, "sb_gemm_tc5: shared memory opt-in failed: %s", cudaGetErrorString(e));
     configured = true;
   }
-  sb_launch<SB_K_TC5>(gemm_tc5_kernel<BN, STAGES, SWAPPED, TO>, dim3(blocks), dim3(THREADS), smem, stream,
+  sb_launch<SB_K_TC5>(gemm_tc5_kernel<BN, STAGES, SWAPPED, TO>, dim3(blocks), dim3(kernel_threads(BN, SWAPPED)), smem, stream,
                   ma, mb, p);
   SB_CHECK_LAUNCH("sb_gemm_tc5");
   return SB_OK;

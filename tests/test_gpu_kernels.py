@@ -123,6 +123,27 @@ def test_linear_epilogues(M, N, K, dtype, kernel):
     assert ops.tc5_status() == 0
 
 
+@pytest.mark.parametrize("M", [1, 2, 7, 16, 33, 63, 64])
+@pytest.mark.parametrize("scale", [1.0, 60.0])
+def test_fused_gate_up_at_few_rows(M, scale):
+    """SiLU(gate) * up from the decode form of the tcgen05 product, whose lanes share the tokens
+    out in twos: odd and even numbers of rows, a last weight tile that is partly outside, and
+    gates beyond -100 and 100 (the exponential overflows: the result is 0, or the up value times
+    the gate)."""
+    N, K = 1040, 200
+    a = rnd(M, K, dtype=torch.bfloat16, scale=scale)
+    w = rnd(N, K, dtype=torch.bfloat16, scale=K ** -0.5, seed=1)
+    out = torch.empty(M, N // 2, dtype=torch.bfloat16, device=DEV)
+    ops.linear(a, w, out, ops.EPI_SWIGLU, kernel="tc5")
+    want = linear_ref(a, w, ops.EPI_SWIGLU, None, None)
+    if scale > 1:
+        gates = (a.double().cpu() @ w.double().cpu().T).view(M, N // 16, 2, 8)[:, :, 0]
+        assert gates.min() < -100 and gates.max() > 100
+    assert torch.isfinite(out).all()
+    close(out, want, 5e-3)
+    assert ops.tc5_status() == 0
+
+
 def _every_epilogue(M, N, K):
     dt = torch.bfloat16
     a, w = rnd(M, K, dtype=dt), rnd(N, K, dtype=dt, scale=K ** -0.5, seed=1)
