@@ -686,18 +686,21 @@ extern "C" int sb_attention(const void* q, void* out, int n_rows, int n_seqs, in
     // the merge of the splits as a kernel of its own.
     const long cache_rows_d = (long)n_pages * 2 * n_kv_heads * KT;
     const long n_items = (long)n_seqs * n_kv_heads * p.n_splits;
-    // It pays when there are many splits.  Measured on B200 at 28/4 heads of 128 and 3,072 keys,
-    // the kernels alone (this one with its merge kernel): 8 sequences 15.1 us the earlier kernel
-    // and 17.0 us this one, 12 sequences 25.2 and 23.5 us, 32 sequences 48.7 and 44.0 us, 64
-    // sequences 87.6 and 77.9 us.  Inside the decode step of a 7B-sized model, where the earlier
-    // kernel's many short blocks overlap the kernels around them better and the merge kernel is
-    // one more launch: 32 sequences 4.24 and 4.28 ms a step, 64 sequences 5.93 and 5.68 ms.  So
-    // from twenty blocks' worth of splits per SM on.  Launched without programmatic dependent
-    // launch: its blocks fill every SM's shared memory, and starting them early cost 0.06 ms a
-    // step at 64 sequences.
+    // It pays when there are many splits.  Measured on B200 at 28/4 heads of 128, the kernels
+    // alone (this one with its merge kernel): 8 sequences of 3,072 keys 15.7 us the earlier kernel
+    // and 15.8 us this one, 16 sequences 27.7 and 25.0 us, 32 sequences 48.8 and 41.5 us, 64
+    // sequences 87.6 and 75.2 us; 8 sequences of 32,768 keys 111 and 92 us.  Inside the decode
+    // step of a 7B-sized model the earlier kernel's many short blocks overlap the kernels around
+    // them better, and the merge kernel is one more launch: 16 sequences around position 6,144
+    // (768 splits) 3.94 and 4.23 ms a step, 8 around 12,288 (768) 3.92 and 3.99 ms, 32 around
+    // 3,072 (1,536) 4.21 and 4.18 ms, 8 around 24,576 (1,536) 5.09 and 4.93 ms, 64 around 3,072
+    // (3,072) 5.93 and 5.68 ms.  So from ten blocks' worth of splits per SM on.  Launched without
+    // programmatic dependent launch: its blocks fill every SM's shared memory, and starting them
+    // early cost 0.02 to 0.06 ms a step at 32 and 64 sequences.
     static bool dt_misaligned = false;
     if (g_force_mma != 1 && !dt_misaligned && n_pages > 0 && n_sms > 0 && cache_rows_d < 2147483647L &&
-        n_items < 2147483647L && (n_items > 20L * n_sms || g_force_mma == 2) && (size_t)2 * DEC_ROWS * p.n_splits * sizeof(float) <= 48 * 1024) {
+        n_items < 2147483647L && (n_items > 10L * n_sms || g_force_mma == 2) && (size_t)(2 * p.n_splits + 3 + DT_MERGE_PARTS * HD) * sizeof(float) <= 48 * 1024 &&
+        n_seqs <= 65535 && max_new * G <= 65535) {
       static bool configured_dt = false;
       if (!configured_dt) {
         cudaError_t e = cudaFuncSetAttribute(attn_decode_tma_kernel,
@@ -732,8 +735,8 @@ extern "C" int sb_attention(const void* q, void* out, int n_rows, int n_seqs, in
         else if (st != 0) SB_FAIL(SB_ERR_CUDA, "sb_attention: a wait in the decode kernel gave up (code %d)", st);
       }
       if (!dt_misaligned && p.n_splits > 1) {
-        sb_launch<SB_K_ATTENTION>(attn_merge_kernel, dim3(n_kv_heads, n_seqs), dim3(DT_MERGE_THREADS),
-                                  (size_t)2 * DEC_ROWS * p.n_splits * sizeof(float), stream, p);
+        sb_launch<SB_K_ATTENTION>(attn_merge_kernel, dim3(n_kv_heads, n_seqs, max_new * G), dim3(DT_MERGE_THREADS),
+                                  (size_t)(2 * p.n_splits + 3 + DT_MERGE_PARTS * HD) * sizeof(float), stream, p);
         SB_CHECK_LAUNCH("sb_attention (split merge)");
         g_last_launches = 2;
       }

@@ -529,7 +529,7 @@ def test_persistent_decode_kernel_finds_a_key_wherever_it_lies():
 
 def test_many_sequences_reach_the_persistent_decode_kernel_by_themselves():
     """96 sequences x 4 key/value heads x 8 splits (one sequence of 1,900 keys sizes the grid, the
-    others have 100 to 700): more than twenty splits per SM on 148 SMs, so "auto" is the
+    others have 100 to 700): more than ten splits per SM on 148 SMs, so "auto" is the
     persistent kernel, which finds most of its work items empty; its rows equal the forced
     kernel's bit for bit, differ from the earlier kernel's by rounding only, and match the plain
     implementation."""
