@@ -40,6 +40,8 @@ CORE = {
     "sb_gemm_tc5_fuses_rope": ("i", "iiiiiiiii"),
     "sb_tc5_status": ("i", ""),
     "sb_gemm_tc5_pairs": ("v", "i"),
+    "sb_gemm_tc5_tile_width": ("i", "iii"),
+    "sb_gemm_tc5_force_width": ("v", "i"),
     "sb_attention_plain": ("i", "ppiippppipiiiiifs"),
     "sb_sample_params_size": ("i", ""),
     "sb_sample": ("i", "piippipps"),

@@ -760,14 +760,22 @@ int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, const Tc5Par
 // 3,584 features on 148 SMs: 256 wide gives 224 tiles (2 waves, the second half empty: 512
 // units), 224 wide 256 tiles (448), 208 wide 288 tiles (1.95 waves: 416).
 constexpr int PERSIST_BNS[] = {256, 240, 224, 208, 192};
-int persistent_bn(int M, int N, int n_sms) {
-  static const int forced = [] {                  // SB_TC5_BN=<width>: one width for every product (for measurements)
+// One tile width for every many-rows product, for measurements and tests: sb_gemm_tc5_force_width
+// sets it (0: by the sizes), SB_TC5_BN=<width> in the environment is its first value.
+int g_forced_bn = -1;
+int valid_bn(int v) {
+  for (int bn : PERSIST_BNS) if (bn == v) return v;
+  return 0;
+}
+int forced_bn() {
+  if (g_forced_bn < 0) {
     const char* e = getenv("SB_TC5_BN");
-    const int v = e ? atoi(e) : 0;
-    for (int bn : PERSIST_BNS) if (bn == v) return v;
-    return 0;
-  }();
-  if (forced) return forced;
+    g_forced_bn = valid_bn(e ? atoi(e) : 0);
+  }
+  return g_forced_bn;
+}
+int persistent_bn(int M, int N, int n_sms) {
+  if (const int forced = forced_bn()) return forced;
   const int tiles_m = (M + BM - 1) / BM;
   int best = 0;
   long best_cost = 0;
@@ -824,14 +832,21 @@ bool pair_enabled() {
   return on;
 }
 
-// Tile width of the pair kernel: as persistent_bn, with 256-row tiles over clusters of two.
-int pair_bn(int M, int N, int clusters) {
-  const int tiles_m = (M + PAIR_M - 1) / PAIR_M;
+// Tile width of the pair kernel.  The prefill products run at the GPU's power limit, where a
+// partly filled last wave of tiles costs next to nothing (the idle SMs' share of the power lets
+// the busy ones clock higher) and what counts is the work per flop: the columns computed beyond
+// N in the last tile, and the operand traffic, which grows as the tile narrows (per flop as
+// 1/width + 1/256; about a third of the energy).  Measured at 2,048 rows, pairs of SMs, widths
+// 256 / 240 / 224 / 208 / 192: 3,584 x 3,584 57 / 70 / 65 / 65 / 71 us, 37,888 x 3,584 415 / 435 /
+// 426 / 438 / 439 us, 4,608 x 3,584 54 / 69 / 80 / 77 / 66 us.  So the widest tile, unless a
+// narrower one leaves clearly fewer columns outside the matrix.
+int pair_bn(int N) {
+  if (const int forced = forced_bn()) return forced;
   int best = 0;
-  long best_cost = 0;
+  double best_cost = 0.0;
   for (int bn : PERSIST_BNS) {
-    const long tiles = (long)tiles_m * ((N + bn - 1) / bn);
-    const long cost = ((tiles + clusters - 1) / clusters) * bn;
+    const double padded = (double)((N + bn - 1) / bn) * bn;
+    const double cost = padded * (1.0 + 0.3 * ((256.0 / bn + 1.0) / 2.0 - 1.0));
     if (!best || cost < best_cost) { best = bn; best_cost = cost; }
   }
   return best;
@@ -846,6 +861,18 @@ extern "C" int sb_tc5_status() { return tc5_read_status(); }
 
 // 1: products of more than 128 rows run on pairs of SMs, 0: on single SMs, -1: by the environment.
 extern "C" void sb_gemm_tc5_pairs(int mode) { g_pair_mode = mode; }
+
+// One of 256, 240, 224, 208, 192: every many-rows product uses that tile width; anything else:
+// the width is chosen by the sizes again.
+extern "C" void sb_gemm_tc5_force_width(int bn) { g_forced_bn = valid_bn(bn); }
+
+// The tile width the product of these sizes runs with in its many-rows form (for tests that
+// want every width covered); 0 when that form does not run.
+extern "C" int sb_gemm_tc5_tile_width(int M, int N, int n_sms) {
+  if (M <= 64 || N < 192 || n_sms <= 0) return 0;
+  if (n_sms > 1 && M > BM && pair_enabled()) return pair_bn(N);
+  return persistent_bn(M, N, n_sms);
+}
 
 namespace {
 
@@ -959,7 +986,7 @@ static int tc5_run(const void* A, int a_dtype, const void* W, int w_dtype, int M
   if (form == 2 && M > 64) SB_FAIL(SB_ERR_UNSUPPORTED, "sb_gemm_tc5: the swapped form takes at most 64 rows");
   if (normal && N >= 192 && n_sms > 1 && M > BM && pair_enabled()) {
     // at least two row tiles, wide output: the persistent kernel on pairs of SMs
-    const int bn = pair_bn(M, N, n_sms / 2);
+    const int bn = pair_bn(N);
     p.tiles_a = (M + PAIR_M - 1) / PAIR_M;
     p.tiles_b = (N + bn - 1) / bn;
     const long n_tiles = (long)p.tiles_a * p.tiles_b;

@@ -135,6 +135,8 @@ int sb_gemm_tc5_fuses_rope(int M, int N, int K, int n_sms, int n_q_heads, int n_
                            int rot, int has_kv);
 int sb_tc5_status(void);      /* 0, or the code of a bounded wait that gave up; clears it */
 void sb_gemm_tc5_pairs(int mode);   /* products of more than 128 rows on pairs of SMs: 1 yes, 0 no, -1 by SB_TC5_PAIR */
+void sb_gemm_tc5_force_width(int bn);   /* 256, 240, 224, 208 or 192 for every many-rows product; else by the sizes */
+int sb_gemm_tc5_tile_width(int M, int N, int n_sms);   /* tile width of the many-rows form; 0: that form does not run */
 
 /* Plain attention over the paged cache (float32 arithmetic, any head size up to 256). */
 int sb_attention_plain(const void* q, void* out, int act_dtype, int n_rows, const int32_t* row_seq,

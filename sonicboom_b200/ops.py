@@ -374,6 +374,19 @@ def tc5_status() -> int:
     return int(lib().sb_tc5_status())
 
 
+def tc5_tile_width(M: int, N: int) -> int:
+    """The tile width the tcgen05 product of M rows and N features runs with in its many-rows
+    form (0: that form does not run): for tests that want every width covered."""
+    sms = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+    return int(lib().sb_gemm_tc5_tile_width(int(M), int(N), sms))
+
+
+def force_tc5_tile_width(width: int) -> None:
+    """256, 240, 224, 208 or 192: every many-rows tcgen05 product uses that tile width (for
+    measurements and tests); 0: chosen by the sizes again."""
+    lib().sb_gemm_tc5_force_width(int(width))
+
+
 def set_tc5_pairs(mode: int) -> None:
     """Whether the tcgen05 product of more than 128 rows runs on pairs of SMs (a cluster of two
     blocks on one 256-row tile): 1 yes, 0 no (one block per 128-row tile), -1 by SB_TC5_PAIR
