@@ -52,6 +52,16 @@ __device__ __forceinline__ __nv_bfloat16 sb_from_f32<__nv_bfloat16>(float v) {
 // (core/src/nn/activation.cpp:41-50, core/src/nn/cuda_elementwise.cu:203-212).
 __device__ __forceinline__ float sb_silu(float x) { return x / (1.0f + expf(-x)); }
 
+// The rotation of one pair (a at index i, b at i + rot/2): lo = a cos - b sin, hi = a sin + b cos,
+// every product and the sum rounded on its own (no fused multiply-add), so that every kernel
+// that rotates gives the same bits whatever the compiler would contract.
+__device__ __forceinline__ float sb_rot_lo(float a, float b, float c, float s) {
+  return __fsub_rn(__fmul_rn(a, c), __fmul_rn(b, s));
+}
+__device__ __forceinline__ float sb_rot_hi(float a, float b, float c, float s) {
+  return __fadd_rn(__fmul_rn(a, s), __fmul_rn(b, c));
+}
+
 __device__ __forceinline__ float sb_warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -321,7 +321,7 @@ __global__ void rope_store_head_kernel(const float* qkv, int n_q_heads, int n_kv
         c = cosf(theta);
         sn = sinf(theta);
       }
-      v = e < half ? src[e] * c - src[e + half] * sn : src[e - half] * sn + src[e] * c;
+      v = e < half ? sb_rot_lo(src[e], src[e + half], c, sn) : sb_rot_hi(src[e - half], src[e], c, sn);
     }
     if (head < n_q_heads)
       q_out[((size_t)t * n_q_heads + head) * hd + e] = sb_from_f32<TQ>(v);
@@ -369,7 +369,7 @@ __global__ void rope_store_kernel(const float* qkv, int n_q_heads, int n_kv_head
     if (!is_v && e < rot) {
       const int i = e < half ? e : e - half;
       const float c = cs[i], sn = cs[half + i];
-      v = e < half ? src[e] * c - src[e + half] * sn : src[e - half] * sn + src[e] * c;
+      v = e < half ? sb_rot_lo(src[e], src[e + half], c, sn) : sb_rot_hi(src[e - half], src[e], c, sn);
     }
     if (head < n_q_heads) {
       q_out[((size_t)t * n_q_heads + head) * hd + e] = sb_from_f32<TQ>(v);
@@ -447,10 +447,10 @@ __global__ void rope_store_vec_kernel(const float* qkv, int n_q_heads, int n_kv_
     } else {
       const float4 c = *reinterpret_cast<const float4*>(cs + e);
       const float4 sn = *reinterpret_cast<const float4*>(cs + half + e);
-      store_bf16x4(dst + e, a.x * c.x - b.x * sn.x, a.y * c.y - b.y * sn.y, a.z * c.z - b.z * sn.z,
-                   a.w * c.w - b.w * sn.w);
-      store_bf16x4(dst + e + half, a.x * sn.x + b.x * c.x, a.y * sn.y + b.y * c.y,
-                   a.z * sn.z + b.z * c.z, a.w * sn.w + b.w * c.w);
+      store_bf16x4(dst + e, sb_rot_lo(a.x, b.x, c.x, sn.x), sb_rot_lo(a.y, b.y, c.y, sn.y),
+                   sb_rot_lo(a.z, b.z, c.z, sn.z), sb_rot_lo(a.w, b.w, c.w, sn.w));
+      store_bf16x4(dst + e + half, sb_rot_hi(a.x, b.x, c.x, sn.x), sb_rot_hi(a.y, b.y, c.y, sn.y),
+                   sb_rot_hi(a.z, b.z, c.z, sn.z), sb_rot_hi(a.w, b.w, c.w, sn.w));
     }
   }
 }

@@ -589,10 +589,10 @@ tc5_reduce_rope_kernel(const Tc5Params p, int bn, const SbRopeStore r) {
     } else {
       const float4 c = *reinterpret_cast<const float4*>(rr_cs + e);
       const float4 sn = *reinterpret_cast<const float4*>(rr_cs + half + e);
-      store4(dst + e, a[0] * c.x - b[0] * sn.x, a[1] * c.y - b[1] * sn.y, a[2] * c.z - b[2] * sn.z,
-             a[3] * c.w - b[3] * sn.w);
-      store4(dst + e + half, a[0] * sn.x + b[0] * c.x, a[1] * sn.y + b[1] * c.y, a[2] * sn.z + b[2] * c.z,
-             a[3] * sn.w + b[3] * c.w);
+      store4(dst + e, sb_rot_lo(a[0], b[0], c.x, sn.x), sb_rot_lo(a[1], b[1], c.y, sn.y),
+             sb_rot_lo(a[2], b[2], c.z, sn.z), sb_rot_lo(a[3], b[3], c.w, sn.w));
+      store4(dst + e + half, sb_rot_hi(a[0], b[0], c.x, sn.x), sb_rot_hi(a[1], b[1], c.y, sn.y),
+             sb_rot_hi(a[2], b[2], c.z, sn.z), sb_rot_hi(a[3], b[3], c.w, sn.w));
     }
   }
 }

@@ -679,6 +679,8 @@ def test_fused_projection_rotation_and_cache_write(hq, hkv, hd, K, rot, rows):
         results.append((q.float().cpu(), storage.float().cpu()))
     (q1, c1), (q2, c2) = results
     assert float(c2.abs().max()) > 0
+    # the same product (to the last bit when the same kernel computes it; the split-K form adds
+    # its partial tiles in another order) and the same rotation arithmetic in every kernel
     assert pm.rel_err(q1, q2) < 4e-3 and pm.rel_err(c1, c2) < 4e-3       # an ulp of bfloat16 at most
     # queries only (a layer that reads another layer's cache)
     qa, qb = torch.empty(rows, hq, hd, dtype=dt, device=DEV), torch.empty(rows, hq, hd, dtype=dt, device=DEV)
