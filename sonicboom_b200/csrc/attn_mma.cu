@@ -535,42 +535,51 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(const AttnP
     den[tid * ns] = 1.0f / sum;
   }
   __syncthreads();
-  for (int item = tid; item < R * (HD / 4); item += DEC_WARPS * 32) {
-    const int row = item / (HD / 4), c = item % (HD / 4);
-    const size_t out_row = (size_t)(row0 + row / G) * p.n_q_heads + kvh * G + row % G;
-    const float* src = p.scratch + (out_row * p.n_splits + split_lo) * PART_STRIDE + 4 * c;
-    const float* w = wgt + row * ns;
-    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    int i = 0;
-    for (; i + 8 <= ns; i += 8) {
-      float4 v[8];
-#pragma unroll
-      for (int u = 0; u < 8; ++u)
-        v[u] = __ldcg(reinterpret_cast<const float4*>(src + (size_t)(i + u) * PART_STRIDE));
+  // A thread takes two of the (row, four values) tasks at a time, DEC_WARPS * 32 apart, and
+  // issues the loads of both before it adds either: the merge is a chain of rounds of L2
+  // latency, and the block that runs it is the last one of its sequence and head.
+  constexpr int MT = DEC_WARPS * 32;
+  for (int item = tid; item < R * (HD / 4); item += 2 * MT) {
+    const bool two = item + MT < R * (HD / 4);
+    const int row_a = item / (HD / 4), c_a = item % (HD / 4);
+    const int row_b = two ? (item + MT) / (HD / 4) : row_a, c_b = two ? (item + MT) % (HD / 4) : c_a;
+    const size_t out_a = (size_t)(row0 + row_a / G) * p.n_q_heads + kvh * G + row_a % G;
+    const size_t out_b = (size_t)(row0 + row_b / G) * p.n_q_heads + kvh * G + row_b % G;
+    const float* src_a = p.scratch + (out_a * p.n_splits + split_lo) * PART_STRIDE + 4 * c_a;
+    const float* src_b = p.scratch + (out_b * p.n_splits + split_lo) * PART_STRIDE + 4 * c_b;
+    const float* w_a = wgt + row_a * ns;
+    const float* w_b = wgt + row_b * ns;
+    float4 acc_a = make_float4(0.0f, 0.0f, 0.0f, 0.0f), acc_b = acc_a;
+    for (int i = 0; i < ns; i += 8) {               // ascending split order, eight of each task at a time
+      float4 va[8], vb[8];
 #pragma unroll
       for (int u = 0; u < 8; ++u) {
-        acc.x = fmaf(v[u].x, w[i + u], acc.x); acc.y = fmaf(v[u].y, w[i + u], acc.y);
-        acc.z = fmaf(v[u].z, w[i + u], acc.z); acc.w = fmaf(v[u].w, w[i + u], acc.w);
-      }
-    }
-    if (i < ns) {                                   // up to seven left: loaded together as well
-      float4 v[7];
-#pragma unroll
-      for (int u = 0; u < 7; ++u)
-        v[u] = i + u < ns ? __ldcg(reinterpret_cast<const float4*>(src + (size_t)(i + u) * PART_STRIDE))
+        const bool in = i + u < ns;
+        va[u] = in ? __ldcg(reinterpret_cast<const float4*>(src_a + (size_t)(i + u) * PART_STRIDE))
+                   : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        vb[u] = in && two ? __ldcg(reinterpret_cast<const float4*>(src_b + (size_t)(i + u) * PART_STRIDE))
                           : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      }
 #pragma unroll
-      for (int u = 0; u < 7; ++u) {
+      for (int u = 0; u < 8; ++u) {
         if (i + u >= ns) break;
-        acc.x = fmaf(v[u].x, w[i + u], acc.x); acc.y = fmaf(v[u].y, w[i + u], acc.y);
-        acc.z = fmaf(v[u].z, w[i + u], acc.z); acc.w = fmaf(v[u].w, w[i + u], acc.w);
+        const float fa = w_a[i + u], fb = w_b[i + u];
+        acc_a.x = fmaf(va[u].x, fa, acc_a.x); acc_a.y = fmaf(va[u].y, fa, acc_a.y);
+        acc_a.z = fmaf(va[u].z, fa, acc_a.z); acc_a.w = fmaf(va[u].w, fa, acc_a.w);
+        acc_b.x = fmaf(vb[u].x, fb, acc_b.x); acc_b.y = fmaf(vb[u].y, fb, acc_b.y);
+        acc_b.z = fmaf(vb[u].z, fb, acc_b.z); acc_b.w = fmaf(vb[u].w, fb, acc_b.w);
       }
     }
-    const float inv = den[row * ns];
+    const float inv_a = den[row_a * ns], inv_b = den[row_b * ns];
     uint2 v;
-    v.x = pack_bf16(acc.x * inv, acc.y * inv);
-    v.y = pack_bf16(acc.z * inv, acc.w * inv);
-    *reinterpret_cast<uint2*>(p.out + out_row * HD + 4 * c) = v;
+    v.x = pack_bf16(acc_a.x * inv_a, acc_a.y * inv_a);
+    v.y = pack_bf16(acc_a.z * inv_a, acc_a.w * inv_a);
+    *reinterpret_cast<uint2*>(p.out + out_a * HD + 4 * c_a) = v;
+    if (two) {
+      v.x = pack_bf16(acc_b.x * inv_b, acc_b.y * inv_b);
+      v.y = pack_bf16(acc_b.z * inv_b, acc_b.w * inv_b);
+      *reinterpret_cast<uint2*>(p.out + out_b * HD + 4 * c_b) = v;
+    }
   }
 }
 
