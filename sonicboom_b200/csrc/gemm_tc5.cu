@@ -1059,11 +1059,16 @@ static int tc5_run(const void* A, int a_dtype, const void* W, int w_dtype, int M
   // copy engine): at most 48 prefetches of 16 KB a block
   if ((size_t)blocks * 48 * SB_WARM_CHUNK < p.warm_bytes) p.warm_bytes = 0;
   int rc;
-  // stages are chosen so that two blocks fit an SM (about 100 KB of shared memory each)
+  // Stages are chosen so that two blocks fit an SM (at most about 100 KB of shared memory each).
+  // At up to 16 rows four stages (72 KB) do as well as six when the kernel runs alone, and leave
+  // room on every SM for a block of the next product, which starts early and requests its first
+  // weight tiles while this one ends: the decode step at batch 8 took 3.073 ms with four stages,
+  // 3.097 with five, 3.104 with six, 3.124 with three (alternating runs on one GPU).  At 32 and
+  // 64 rows fewer stages were slower (batch 64: 5.445 ms with three, 5.380 with four).
 #define SB_TC5_SWAPPED(BN_, ST_)                                                             \
   rc = out_dtype == SB_F32 ? launch<BN_, ST_, true, float>(ma, mb, p, blocks, stream)         \
                            : launch<BN_, ST_, true, bf16>(ma, mb, p, blocks, stream);
-  if (bn == 16) { SB_TC5_SWAPPED(16, 6) }
+  if (bn == 16) { SB_TC5_SWAPPED(16, 4) }
   else if (bn == 32) { SB_TC5_SWAPPED(32, 5) }
   else { SB_TC5_SWAPPED(64, 4) }
 #undef SB_TC5_SWAPPED
