@@ -531,6 +531,34 @@ def test_persistent_decode_kernel_finds_a_key_wherever_it_lies():
         assert abs(float(out.mean()) - (key_pos + 1)) < 0.02 * (key_pos + 1), (key_pos, float(out.mean()))
 
 
+@pytest.mark.parametrize("kernel", ["tma", "mma"])
+def test_decode_over_forty_splits(kernel):
+    """A sequence of 20,001 keys (40 splits of 512) beside one of 9,000 (18) and a short one: the
+    merge of the splits goes through several rounds of loads and, after the persistent kernel,
+    through thread groups with ten, ten, ten and ten splits (five, five, five and three for the
+    second sequence).  One key stands out, in the first, a middle or the last split; then
+    random rows against the plain implementation."""
+    hq, hkv, hd = 4, 2, 128
+    lens = [20001, 9000, 70]
+    for key_pos in (5, 5000, 10300, 15500, 19990):
+        cache = make_cache(hkv, hd, 0, torch.bfloat16, max_tokens=64 * 320)
+        x = standout(lens[0], hq, hkv, hd, key_pos)
+        s = cache.open()
+        run_attention(cache, hq, hkv, hd, 0, torch.bfloat16, [(s, x[:-1])], rot=0)
+        out, _ = run_attention(cache, hq, hkv, hd, 0, torch.bfloat16, [(s, x[-1:])], rot=0, kernel=kernel)
+        assert abs(float(out.mean()) - (key_pos + 1)) < 0.02 * (key_pos + 1), (key_pos, float(out.mean()))
+    cache = make_cache(hkv, hd, 0, torch.bfloat16, max_tokens=64 * 470)
+    xs = [torch.randn(n + 1, (hq + 2 * hkv) * hd, generator=torch.Generator().manual_seed(n)) * 0.5 for n in lens]
+    slots = [cache.open() for _ in lens]
+    for s, x, n in zip(slots, xs, lens):
+        run_attention(cache, hq, hkv, hd, 0, torch.bfloat16, [(s, x[:n])])
+    out, _ = run_attention(cache, hq, hkv, hd, 0, torch.bfloat16, [(s, x[n:]) for s, x, n in zip(slots, xs, lens)],
+                           kernel=kernel)
+    for i, (x, n) in enumerate(zip(xs, lens)):
+        close(out[i:i + 1], attention_ref(x[n:], n, hq, hkv, hd, 0, history=x[:n]), 1.5e-2)
+    assert ops.attention_status(hd) == 0
+
+
 def test_many_sequences_reach_the_persistent_decode_kernel_by_themselves():
     """96 sequences x 4 key/value heads x 8 splits (one sequence of 1,900 keys sizes the grid, the
     others have 100 to 700): more than ten splits per SM on 148 SMs, so "auto" is the
