@@ -886,7 +886,7 @@ int pair_clusters() {
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2);
-  cfg.blockDim = dim3(THREADS);
+  cfg.blockDim = dim3(PAIR_THREADS);
   cfg.dynamicSmemBytes = smem;
   int n = 0;
   if (cudaOccupancyMaxActiveClusters(&n, gemm_tc5_pair_kernel<BN, PAIR_STAGES, TO>, &cfg) == cudaSuccess && n > 0)
@@ -899,7 +899,7 @@ int pair_clusters() {
 template <int BN, typename TO>
 int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const Tc5Params& p, int clusters,
                 cudaStream_t stream) {
-  sb_launch<SB_K_TC5>(gemm_tc5_pair_kernel<BN, PAIR_STAGES, TO>, dim3(2 * clusters), dim3(THREADS),
+  sb_launch<SB_K_TC5>(gemm_tc5_pair_kernel<BN, PAIR_STAGES, TO>, dim3(2 * clusters), dim3(PAIR_THREADS),
                       pair_smem_bytes(BN, PAIR_STAGES), stream, ma, mb, p);
   SB_CHECK_LAUNCH("sb_gemm_tc5 (pairs)");
   return SB_OK;

@@ -26,17 +26,23 @@ namespace {
 
 constexpr int PAIR_M = 2 * BM;
 constexpr int PAIR_STAGES = 6;
+// Two groups of four epilogue warps per block (a warp reaches its quarter of the tensor memory's
+// lanes only): the groups take alternate 32-column chunks of the tile, which halves the time the
+// last tile's epilogue, hidden behind nothing, takes.
+constexpr int PAIR_EPI_GROUPS = 2;
+constexpr int PAIR_THREADS = 64 + 128 * PAIR_EPI_GROUPS;
 constexpr int pair_stage_bytes(int bn) { return (BM + bn / 2) * BK * 2; }
 constexpr int pair_smem_bytes(int bn, int stages) {
-  return stages * pair_stage_bytes(bn) + PERSIST_STAGING + 1024 + 256;
+  return stages * pair_stage_bytes(bn) + PAIR_EPI_GROUPS * PERSIST_STAGING + 1024 + 256;
 }
+static_assert(pair_smem_bytes(256, PAIR_STAGES) <= 232448, "the pair kernel's shared memory");
 // float32 accumulator, bfloat16 A and B, both K-major, M = 256 over the pair, N = bn
 __host__ __device__ constexpr uint32_t pair_instr_desc(int bn) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(PAIR_M >> 4) << 24);
 }
 
 template <int BN, int STAGES, typename TO>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS)
 gemm_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_a,
                      const __grid_constant__ CUtensorMap map_b, const Tc5Params p) {
   static_assert(BN % 16 == 0 && BN <= 256, "the MMA's width");
@@ -45,7 +51,7 @@ gemm_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_a,
   const uint32_t raw = (uint32_t)__cvta_generic_to_shared(smem_raw);
   const uint32_t tiles = (raw + 1023u) & ~1023u;
   const uint32_t staging = tiles + STAGES * pair_stage_bytes(BN);
-  const uint32_t bars = staging + PERSIST_STAGING;
+  const uint32_t bars = staging + PAIR_EPI_GROUPS * PERSIST_STAGING;
   const uint32_t full0 = bars, empty0 = bars + 8 * STAGES;
   const uint32_t acc_full0 = bars + 16 * STAGES, acc_empty0 = acc_full0 + 16;
   const uint32_t tmem_slot = acc_empty0 + 16;
@@ -66,7 +72,7 @@ gemm_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_a,
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(acc_full0 + 8 * a, 1);
-      mbar_init(acc_empty0 + 8 * a, 8);                // one arrival per epilogue warp of both blocks
+      mbar_init(acc_empty0 + 8 * a, 8 * PAIR_EPI_GROUPS);   // one arrival per epilogue warp of both blocks
     }
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
@@ -133,7 +139,7 @@ gemm_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_a,
     // ---- epilogue (both blocks): this warp reads TMEM lanes [32 q, 32 q + 32) of this block's
     // half of the finished accumulator
     sb_pdl_wait();
-    const int q = warp & 3;
+    const int q = warp & 3, group = (warp - 2) >> 2;
     float* stage = reinterpret_cast<float*>(smem_raw + (staging - raw)) + (warp - 2) * 32 * 33;
     const uint32_t acc_empty_of_0 = map_to_block(acc_empty0, 0);
     uint32_t lt = 0;
@@ -145,13 +151,13 @@ gemm_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_a,
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + acc * ACC_COLS;
       const int m_base = tile_a * PAIR_M + (int)rank * BM + q * 32;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = group; c < BN / 32; c += PAIR_EPI_GROUPS) {
         uint32_t r[32];
         tmem_ld32(t_row + c * 32, r);
         const int n0 = tile_b * BN + c * 32;
         if (n0 < p.N) store_chunk<TO>(p, stage, r, m_base, n0, lane);
       }
-      if (BN % 32) {                                   // a last chunk of 16 columns
+      if (BN % 32 && group == (BN / 32) % PAIR_EPI_GROUPS) {   // a last chunk of 16 columns
         uint32_t r[32];
         tmem_ld16(t_row + (BN / 32) * 32, r);
         const int n0 = tile_b * BN + (BN / 32) * 32;
