@@ -34,11 +34,12 @@ typedef __nv_bfloat16 bf16;
 
 constexpr int BM = 128, BK = 64, UMMA_K = 16;
 constexpr int THREADS = 192;
-// The decode form with 64 tokens has two groups of four epilogue warps: a warp reaches only its
-// own quarter of the tensor memory's lanes (weight rows), so the second group takes the second
-// half of the columns (tokens).  With one group the epilogue of the last wave of blocks, beside
-// which nothing else runs, took 5 of the fused gate/up product's 46 microseconds.
-constexpr int epilogue_groups(int bn, bool swapped) { return swapped && bn == 64 ? 2 : 1; }
+// The decode form with 32 or 64 tokens has two groups of four epilogue warps: a warp reaches only
+// its own quarter of the tensor memory's lanes (weight rows), so the second group takes the
+// second half of the columns (tokens).  With one group the epilogue of the last wave of blocks,
+// beside which nothing else runs, took 5 of the fused gate/up product's 46 microseconds at 64
+// tokens (at 32 tokens the second group is worth 0.2 % of the decode step).
+constexpr int epilogue_groups(int bn, bool swapped) { return swapped && bn >= 32 ? 2 : 1; }
 constexpr int kernel_threads(int bn, bool swapped) { return 64 + 128 * epilogue_groups(bn, swapped); }
 // Shared-memory matrix descriptor of a K-major tile with the 128-byte swizzle: rows of 128
 // bytes, groups of 8 rows 1024 bytes apart.
