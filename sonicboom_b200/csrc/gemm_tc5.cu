@@ -3,20 +3,25 @@
 // with tcgen05.ld.  out[M,N] = A[M,K] . W[N,K]^T with the fused epilogues of gemm_plain.cu.
 //
 // One block computes a 128 x BN tile.  Warp 0 is the TMA producer, warp 1 allocates tensor
-// memory and issues the MMAs, warps 2-5 run the epilogue (one TMEM lane quarter each).  Both
+// memory and issues the MMAs, warps 2-5 run the epilogue (one TMEM lane quarter each; the decode
+// form from 32 tokens on has warps 6-9 as a second group).  Both
 // operands are K-major; tiles are 64 values (128 bytes) wide in K and stored with the 128-byte
 // swizzle that the tensor maps write and the MMA descriptors read.  Rows and columns beyond
 // M, N and K are zero-filled by TMA, so any M and N and any K that is a multiple of 8 work.
 //
 // Two forms share the kernel:
-//   normal   A = activations (rows are tokens), B = weights: the prefill product;
+//   normal   A = activations (rows are tokens), B = weights: the prefill product.  With many
+//            rows it is a persistent kernel (further down), from 129 rows on one on pairs of SMs
+//            (gemm_tc5_pair.cuh); their epilogue keeps a thread's row and writes 16 bytes at a
+//            time along it (store_chunk_rowwise);
 //   swapped  A = weights (128 weight rows per tile), B = activations (up to 64 rows): the
 //            decode product, which is bound by reading the weights once.  K may be split over
 //            several blocks; their partial tiles go to scratch memory and a second kernel adds
 //            them in split order and runs the epilogue, so the sum's order is fixed.  That
 //            second kernel can also apply the RMSNorm that follows the product
 //            (tc5_reduce_norm_kernel: a cluster of blocks per row, the sum of squares over
-//            distributed shared memory).
+//            distributed shared memory), or the rotation and the cache write that follow a
+//            q|k|v product (tc5_reduce_rope_kernel).
 //
 // Every wait on an mbarrier is bounded; when a bound is hit the kernel records a code in a
 // status word, stops issuing work and leaves normally (sb_tc5_status reads the word).

@@ -17,7 +17,7 @@
 //   empty[s]     one in each block, for that block's producer; block 0's MMA thread commits to
 //                both at once (`tcgen05.commit ... multicast::cluster`).
 //   acc_full[a]  one in each block, for that block's epilogue warps; committed to both at once.
-//   acc_empty[a] block 0's only; the four epilogue warps of both blocks arrive on it.
+//   acc_empty[a] block 0's only; the eight epilogue warps of both blocks arrive on it.
 // Every wait is bounded; a block whose wait runs out records a code, stops issuing and goes to
 // the common end, where the two blocks meet before tensor memory is given back.
 #pragma once
