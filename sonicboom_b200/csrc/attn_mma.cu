@@ -309,16 +309,22 @@ __global__ void __launch_bounds__(PREFILL_THREADS) attn_prefill_kernel(const Att
 // are done the tiles' space is reused for the warps' partial outputs.
 // K/V tiles in flight or in use.  Two: three blocks fit an SM, and their staggered stalls cover
 // each other; three or four stages (two blocks or one per SM) measured 20.6 and 22.8 us
-// against 14.9 us per layer at batch 8, 3,072 keys, whatever the split length.
-constexpr int DEC_STAGES = 2;
+// against 14.9 us per layer at batch 8, 3,072 keys, whatever the split length.  When the whole
+// grid is at most a block per SM (one to three sequences of the benchmark model) nothing covers
+// a block's stalls but its own loads in flight: then four stages (DEC_STAGES_FEW), which take a
+// 256-key split's tiles all at once.  The tiles are used in the same order either way.
+constexpr int DEC_STAGES = 2, DEC_STAGES_FEW = 4;
 constexpr size_t WARM_MAX_CHUNKS = 48;   // most 16 KB prefetches a block issues for the L2 hint
-constexpr int DECODE_SMEM = (DEC_ROWS + 2 * DEC_STAGES * KT) * LDS * 2;
+constexpr int decode_smem(int stages) { return (DEC_ROWS + 2 * stages * KT) * LDS * 2; }
+constexpr int DECODE_SMEM = decode_smem(DEC_STAGES);
 constexpr int PART_STRIDE = HD + 4;    // floats per partial row: o[HD], m, l (rows stay 16-byte aligned)
 constexpr bool DECODE_FITS = DECODE_SMEM <= 227 * 1024;
+constexpr bool DECODE_FEW_FITS = decode_smem(DEC_STAGES_FEW) <= 227 * 1024;
 static_assert(DEC_WARPS * 16 == KT, "each warp takes 16 keys of a tile");
 static_assert((DEC_WARPS * DEC_ROWS * PART_STRIDE + (DEC_WARPS + 2) * DEC_ROWS) * 4 <= 2 * DEC_STAGES * KT * LDS * 2,
               "partials and weights fit the tiles");
 
+template <int STAGES>
 __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(const AttnParams p) {
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ int s_last;
@@ -376,7 +382,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(const AttnP
   }
   cp_async_commit();                                  // group: the query rows
 #pragma unroll
-  for (int i = 1; i < DEC_STAGES; ++i) {              // groups: the next tiles
+  for (int i = 1; i < STAGES; ++i) {              // groups: the next tiles
     if (i < LONG_SPLIT_PAGES && tile_lo + i <= tile_hi)
       load_kv_tile(kv0 + i * 2 * KT * LDS * 2, kv0 + (i * 2 + 1) * KT * LDS * 2, p.cache, page_of[i],
                    p.n_kv_heads, kvh, tid, DEC_WARPS * 32);
@@ -394,9 +400,9 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(const AttnP
   uint32_t qf[HD / 16][4];
 
   for (int tile = tile_lo; tile <= tile_hi; ++tile) {
-    const int stage = (tile - tile_lo) % DEC_STAGES;
+    const int stage = (tile - tile_lo) % STAGES;
     const uint32_t ks = kv0 + stage * 2 * KT * LDS * 2, vs = ks + KT * LDS * 2;
-    cp_async_wait<DEC_STAGES - 1>();                  // this tile has landed; the next may be in flight
+    cp_async_wait<STAGES - 1>();                  // this tile has landed; the next may be in flight
     __syncthreads();
     if (tile == tile_lo) load_q_frags(qs, 0, lane, qf);
     // this warp's 16 keys of the tile
@@ -404,11 +410,11 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(const AttnP
     tile_step<16>(qf, ks + off, vs + off, tile * KT + warp * 16, pos_a, pos_b, p.window, p.scale_log2,
                   m, l, o, lane);
     __syncthreads();                                  // the stage is free: request a later tile into it
-    if (tile + DEC_STAGES <= tile_hi) {
+    if (tile + STAGES <= tile_hi) {
       int pg = page_of[0];
 #pragma unroll
       for (int i = 1; i < LONG_SPLIT_PAGES; ++i)
-        if (tile + DEC_STAGES - tile_lo == i) pg = page_of[i];
+        if (tile + STAGES - tile_lo == i) pg = page_of[i];
       load_kv_tile(ks, vs, p.cache, pg, p.n_kv_heads, kvh, tid, DEC_WARPS * 32);
     }
     cp_async_commit();
@@ -671,8 +677,11 @@ extern "C" int sb_attention(const void* q, void* out, int n_rows, int n_seqs, in
     cudaError_t e1 = cudaFuncSetAttribute(attn_prefill_kernel,
                                           cudaFuncAttributeMaxDynamicSharedMemorySize, PREFILL_SMEM);
     cudaError_t e2 = !DECODE_FITS ? cudaSuccess :
-        cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaFuncSetAttribute(attn_decode_kernel<DEC_STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              DECODE_SMEM);
+    if (e2 == cudaSuccess && DECODE_FEW_FITS)
+      e2 = cudaFuncSetAttribute(attn_decode_kernel<DEC_STAGES_FEW>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                decode_smem(DEC_STAGES_FEW));
     if (e1 != cudaSuccess || e2 != cudaSuccess)
       SB_FAIL(SB_ERR_CUDA, "sb_attention: shared memory opt-in failed: %s",
               cudaGetErrorString(e1 != cudaSuccess ? e1 : e2));
@@ -754,8 +763,12 @@ extern "C" int sb_attention(const void* q, void* out, int n_rows, int n_seqs, in
 #endif
     if ((size_t)p.n_splits * n_kv_heads * n_seqs * WARM_MAX_CHUNKS * SB_WARM_CHUNK < p.warm_bytes)
       p.warm_bytes = 0;
-    sb_launch<SB_K_ATTENTION>(attn_decode_kernel, dim3(p.n_splits, n_kv_heads, n_seqs), dim3(DEC_WARPS * 32),
-              DECODE_SMEM, stream, p);
+    if (DECODE_FEW_FITS && n_sms > 0 && (long)p.n_splits * n_kv_heads * n_seqs <= n_sms)
+      sb_launch<SB_K_ATTENTION>(attn_decode_kernel<DEC_STAGES_FEW>, dim3(p.n_splits, n_kv_heads, n_seqs),
+                                dim3(DEC_WARPS * 32), decode_smem(DEC_STAGES_FEW), stream, p);
+    else
+      sb_launch<SB_K_ATTENTION>(attn_decode_kernel<DEC_STAGES>, dim3(p.n_splits, n_kv_heads, n_seqs),
+                                dim3(DEC_WARPS * 32), DECODE_SMEM, stream, p);
     SB_CHECK_LAUNCH("sb_attention (decode)");
     return SB_OK;
   }
@@ -874,7 +887,7 @@ extern "C" int sb_attention_decode_static(const void* q, void* out, int n_rows, 
     e = cudaGetSymbolAddress(&ptr, g_static_scratch);
     if (e != cudaSuccess || !ptr)
       SB_FAIL(SB_ERR_CUDA, "%s: cudaGetSymbolAddress: %s", who, cudaGetErrorString(e));
-    e = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    e = cudaFuncSetAttribute(attn_decode_kernel<DEC_STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              DECODE_SMEM);
     if (e != cudaSuccess)
       SB_FAIL(SB_ERR_CUDA, "%s: shared memory opt-in failed: %s", who, cudaGetErrorString(e));
@@ -895,7 +908,7 @@ extern "C" int sb_attention_decode_static(const void* q, void* out, int n_rows, 
   p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads; p.window = window; p.n_splits = n_splits;
   p.n_seqs = n_seqs;
   p.scale_log2 = scale * LOG2E;
-  sb_launch<SB_K_ATTENTION>(attn_decode_kernel, dim3(n_splits, n_kv_heads, n_seqs), dim3(DEC_WARPS * 32), DECODE_SMEM,
+  sb_launch<SB_K_ATTENTION>(attn_decode_kernel<DEC_STAGES>, dim3(n_splits, n_kv_heads, n_seqs), dim3(DEC_WARPS * 32), DECODE_SMEM,
             stream, p);
   SB_CHECK_LAUNCH("sb_attention_decode_static (decode)");
   return SB_OK;
