@@ -312,14 +312,19 @@ __global__ void __launch_bounds__(PREFILL_THREADS) attn_prefill_kernel(const Att
 // against 14.9 us per layer at batch 8, 3,072 keys, whatever the split length.  When the whole
 // grid is at most a block per SM (one to three sequences of the benchmark model) nothing covers
 // a block's stalls but its own loads in flight: then four stages (DEC_STAGES_FEW), which take a
-// 256-key split's tiles all at once.  The tiles are used in the same order either way.
-constexpr int DEC_STAGES = 2, DEC_STAGES_FEW = 4;
+// 256-key split's tiles all at once; with at most two blocks per SM three stages
+// (DEC_STAGES_SOME: two such blocks fit an SM).  Inside the decode step of a 7B-sized model:
+// batch 1 2.888 to 2.849 ms, batch 2 2.935 to 2.858, batch 4 3.000 to 2.958, batch 5 3.014 to
+// 2.972; batch 3 and batch 6, whose grids all but fill the SMs at that rate, unchanged.  The
+// tiles are used in the same order whatever the number of stages.
+constexpr int DEC_STAGES = 2, DEC_STAGES_SOME = 3, DEC_STAGES_FEW = 4;
 constexpr size_t WARM_MAX_CHUNKS = 48;   // most 16 KB prefetches a block issues for the L2 hint
 constexpr int decode_smem(int stages) { return (DEC_ROWS + 2 * stages * KT) * LDS * 2; }
 constexpr int DECODE_SMEM = decode_smem(DEC_STAGES);
 constexpr int PART_STRIDE = HD + 4;    // floats per partial row: o[HD], m, l (rows stay 16-byte aligned)
 constexpr bool DECODE_FITS = DECODE_SMEM <= 227 * 1024;
 constexpr bool DECODE_FEW_FITS = decode_smem(DEC_STAGES_FEW) <= 227 * 1024;
+constexpr bool DECODE_SOME_FITS = 2 * (decode_smem(DEC_STAGES_SOME) + 1024) <= 228 * 1024;   // two blocks per SM
 static_assert(DEC_WARPS * 16 == KT, "each warp takes 16 keys of a tile");
 static_assert((DEC_WARPS * DEC_ROWS * PART_STRIDE + (DEC_WARPS + 2) * DEC_ROWS) * 4 <= 2 * DEC_STAGES * KT * LDS * 2,
               "partials and weights fit the tiles");
@@ -682,6 +687,9 @@ extern "C" int sb_attention(const void* q, void* out, int n_rows, int n_seqs, in
     if (e2 == cudaSuccess && DECODE_FEW_FITS)
       e2 = cudaFuncSetAttribute(attn_decode_kernel<DEC_STAGES_FEW>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                 decode_smem(DEC_STAGES_FEW));
+    if (e2 == cudaSuccess && DECODE_SOME_FITS)
+      e2 = cudaFuncSetAttribute(attn_decode_kernel<DEC_STAGES_SOME>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                decode_smem(DEC_STAGES_SOME));
     if (e1 != cudaSuccess || e2 != cudaSuccess)
       SB_FAIL(SB_ERR_CUDA, "sb_attention: shared memory opt-in failed: %s",
               cudaGetErrorString(e1 != cudaSuccess ? e1 : e2));
@@ -766,6 +774,9 @@ extern "C" int sb_attention(const void* q, void* out, int n_rows, int n_seqs, in
     if (DECODE_FEW_FITS && n_sms > 0 && (long)p.n_splits * n_kv_heads * n_seqs <= n_sms)
       sb_launch<SB_K_ATTENTION>(attn_decode_kernel<DEC_STAGES_FEW>, dim3(p.n_splits, n_kv_heads, n_seqs),
                                 dim3(DEC_WARPS * 32), decode_smem(DEC_STAGES_FEW), stream, p);
+    else if (DECODE_SOME_FITS && n_sms > 0 && (long)p.n_splits * n_kv_heads * n_seqs <= 2L * n_sms)
+      sb_launch<SB_K_ATTENTION>(attn_decode_kernel<DEC_STAGES_SOME>, dim3(p.n_splits, n_kv_heads, n_seqs),
+                                dim3(DEC_WARPS * 32), decode_smem(DEC_STAGES_SOME), stream, p);
     else
       sb_launch<SB_K_ATTENTION>(attn_decode_kernel<DEC_STAGES>, dim3(p.n_splits, n_kv_heads, n_seqs),
                                 dim3(DEC_WARPS * 32), DECODE_SMEM, stream, p);
