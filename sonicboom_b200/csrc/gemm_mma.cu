@@ -52,7 +52,10 @@ __device__ __forceinline__ float load_bias(const void* bias, int n) {
 
 // ------------------------------------------------------------------------------- skinny
 constexpr int SK_WARPS = 8;      // warps of a block; they split K
-constexpr int SK_UNROLL = 4;     // 32-wide K blocks a warp has in flight
+// 32-wide K blocks a warp has in flight.  Inside the decode step of a 7B-sized model (the q|k|v
+// projection at up to 8 rows): batch 1 2.896 ms with two, 2.850 with four, 2.830 with eight,
+// 2.847 with twelve, 2.905 with sixteen; batch 8 3.115 / 3.073 / 3.064 / 3.072 / 3.130.
+constexpr int SK_UNROLL = 8;
 
 // W is the MMA's A operand (16 rows of W), the activations its B operand (8 rows each).
 // Within a 32-wide K block, thread t of a quad loads the 8 consecutive values k0+8t..k0+8t+7
