@@ -931,8 +931,18 @@ bool pair_enabled() {
 // 256 / 240 / 224 / 208 / 192: 3,584 x 3,584 57 / 70 / 65 / 65 / 71 us, 37,888 x 3,584 415 / 435 /
 // 426 / 438 / 439 us, 4,608 x 3,584 54 / 69 / 80 / 77 / 66 us.  So the widest tile, unless a
 // narrower one leaves clearly fewer columns outside the matrix.
-int pair_bn(int N) {
+int pair_bn(int M, int N, int clusters) {
   if (const int forced = forced_bn()) return forced;
+  // Few rows: when even the widest tiles do not give every pair of SMs one, the product takes as
+  // long as one tile does, and the narrowest width that still fits one wave wins (512 rows,
+  // 3,584 x 18,944: 122 us at 256 columns, 108 us at 192).
+  const long tiles_m = (M + PAIR_M - 1) / PAIR_M;
+  if (clusters > 0 && tiles_m * ((N + 255) / 256) <= clusters) {
+    int narrow = 256;
+    for (int bn : PERSIST_BNS)
+      if (tiles_m * ((N + bn - 1) / bn) <= clusters && bn < narrow) narrow = bn;
+    return narrow;
+  }
   int best = 0;
   double best_cost = 0.0;
   for (int bn : PERSIST_BNS) {
@@ -961,7 +971,7 @@ extern "C" void sb_gemm_tc5_force_width(int bn) { g_forced_bn = valid_bn(bn); }
 // want every width covered); 0 when that form does not run.
 extern "C" int sb_gemm_tc5_tile_width(int M, int N, int n_sms) {
   if (M <= 64 || N < 192 || n_sms <= 0) return 0;
-  if (n_sms > 1 && M > BM && pair_enabled()) return pair_bn(N);
+  if (n_sms > 1 && M > BM && pair_enabled()) return pair_bn(M, N, n_sms / 2);
   return persistent_bn(M, N, n_sms);
 }
 
@@ -1081,7 +1091,7 @@ static int tc5_run(const void* A, int a_dtype, const void* W, int w_dtype, int M
   if (form == 2 && M > 64) SB_FAIL(SB_ERR_UNSUPPORTED, "sb_gemm_tc5: the swapped form takes at most 64 rows");
   if (normal && N >= 192 && n_sms > 1 && M > BM && pair_enabled()) {
     // at least two row tiles, wide output: the persistent kernel on pairs of SMs
-    const int bn = pair_bn(N);
+    const int bn = pair_bn(M, N, n_sms / 2);
     p.tiles_a = (M + PAIR_M - 1) / PAIR_M;
     p.tiles_b = (N + bn - 1) / bn;
     const long n_tiles = (long)p.tiles_a * p.tiles_b;

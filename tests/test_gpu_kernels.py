@@ -174,15 +174,16 @@ def test_persistent_product_at_every_tile_width(M, N, K):
         ops.set_tc5_pairs(-1)
 
 
-PAIR_SIZES = [(1280, 3376, 72, 256), (1280, 1184, 72, 240), (1280, 1104, 72, 224), (1280, 2064, 136, 208),
-              (300, 560, 328, 192), (129, 528, 64, 192), (2048, 4608, 1032, 256)]
+PAIR_SIZES = [(1280, 3376, 72, 256), (1280, 3152, 72, 240), (1280, 2928, 72, 224), (1280, 2720, 136, 208),
+              (300, 560, 328, 192), (129, 528, 64, 192), (2048, 4608, 1032, 256), (2048, 3600, 136, 240)]
 
 
 @pytest.mark.parametrize("M,N,K,width", PAIR_SIZES)
 def test_product_on_pairs_of_sms(M, N, K, width):
     """The same product on clusters of two blocks (one MMA of 256 rows over two SMs), at sizes for
-    which it picks each of its tile widths, all with a last tile that is partly outside the
-    matrix: rows that end inside the first block's half of a tile (129), inside the second's (300:
+    which it picks each of its tile widths (the narrowest that gives the 74 pairs one wave when
+    there are few rows; by the work per flop in the last two), all with a last tile that is partly
+    outside the matrix: rows that end inside the first block's half of a tile (129), inside the second's (300:
     the second tile's second block loads nothing but zeros), several K tiles per stage of the
     ring (1,032 = 17 tiles, the last one of 8 values).  Every epilogue against the float64
     product, and the same bits as one block per tile gives."""
