@@ -955,6 +955,25 @@ int pair_bn(int M, int N, int clusters) {
 
 }  // namespace
 
+namespace {
+// K splits of the pair kernel.  When even 256-column tiles leave at least half of the pairs of
+// SMs without one and the inner dimension is long enough, every tile's K blocks are shared out
+// over as many pairs as there are to spare (at most eight, at least eight K blocks each); the
+// tiles are then 256 columns wide.  1: no split.
+int pair_splits(int M, int N, int K, int clusters) {
+  if (forced_bn() || N % 16) return 1;
+  const long tiles = (long)((M + PAIR_M - 1) / PAIR_M) * ((N + 255) / 256);
+  const int n_k = (K + BK - 1) / BK;
+  if (clusters <= 0 || 2 * tiles > clusters) return 1;
+  int splits = (int)(clusters / tiles);
+  if (splits > 8) splits = 8;
+  if (splits > n_k / 8) splits = n_k / 8;
+  if (splits < 2) return 1;
+  const int k_per = (n_k + splits - 1) / splits;
+  return (n_k + k_per - 1) / k_per;
+}
+}  // namespace
+
 // 0 when no kernel has given up on a wait since the last call; else the code of the wait
 // (1 producer/empty, 2 producer drain, 3 MMA/full, 4 epilogue/accumulator).  Reading
 // synchronizes with the device.
@@ -995,7 +1014,13 @@ int choose_splits(int N, int K, int n_sms) {
 
 // Bytes of scratch (partial tiles) the swapped form needs for these sizes; 0 when K is not split.
 extern "C" size_t sb_gemm_tc5_scratch_bytes(int M, int N, int K, int n_sms) {
-  if (M > 64 || M <= 0 || N <= 0 || K <= 0) return 0;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (M > BM && N >= 192 && n_sms > 1 && pair_enabled()) {
+    // the many-rows form on pairs of SMs, when it splits K: [split][row][column]
+    const int splits = pair_splits(M, N, K, n_sms / 2);
+    return splits > 1 ? (size_t)splits * M * N * sizeof(float) : 0;
+  }
+  if (M > 64) return 0;
   const int splits = choose_splits(N, K, n_sms);
   if (splits <= 1) return 0;
   const int tiles = (N + BM - 1) / BM;
@@ -1091,10 +1116,15 @@ static int tc5_run(const void* A, int a_dtype, const void* W, int w_dtype, int M
   if (form == 2 && M > 64) SB_FAIL(SB_ERR_UNSUPPORTED, "sb_gemm_tc5: the swapped form takes at most 64 rows");
   if (normal && N >= 192 && n_sms > 1 && M > BM && pair_enabled()) {
     // at least two row tiles, wide output: the persistent kernel on pairs of SMs
-    const int bn = pair_bn(M, N, n_sms / 2);
+    int splits = p.rowwise ? pair_splits(M, N, K, n_sms / 2) : 1;
+    if (splits > 1 && (!scratch || scratch_bytes < (size_t)splits * M * N * sizeof(float) || ((uintptr_t)scratch & 255)))
+      splits = 1;                                       // no room for the partial sums: the whole K per tile
+    const int bn = splits > 1 ? 256 : pair_bn(M, N, n_sms / 2);
+    p.k_splits = splits;
+    p.scratch = splits > 1 ? (float*)scratch : nullptr;
     p.tiles_a = (M + PAIR_M - 1) / PAIR_M;
     p.tiles_b = (N + bn - 1) / bn;
-    const long n_tiles = (long)p.tiles_a * p.tiles_b;
+    const long n_tiles = (long)p.tiles_a * p.tiles_b * splits;
     if (n_tiles > 2147483647L) SB_FAIL(SB_ERR_UNSUPPORTED, "sb_gemm_tc5: too many tiles");
     int clusters = 0;
 #define SB_TC5_PAIR_CLUSTERS(BN_)                                                                  \
@@ -1102,10 +1132,21 @@ static int tc5_run(const void* A, int a_dtype, const void* W, int w_dtype, int M
     SB_TC5_PAIR_CLUSTERS(256) SB_TC5_PAIR_CLUSTERS(240) SB_TC5_PAIR_CLUSTERS(224) SB_TC5_PAIR_CLUSTERS(208)
     SB_TC5_PAIR_CLUSTERS(192)
 #undef SB_TC5_PAIR_CLUSTERS
+    if (splits > 1) clusters = pair_clusters<256, float>();   // the kernel that writes the partial sums
     if (clusters > 0) {                               // else: the one-block kernel below
       if (!make_map(&ma, A, M, K, BM) || !make_map(&mb, W, N, K, bn / 2))
         SB_FAIL(SB_ERR_CUDA, "sb_gemm_tc5: cuTensorMapEncodeTiled failed");
       if (n_tiles < clusters) clusters = (int)n_tiles;
+      if (splits > 1) {
+        // the partial sums, then their sum in split order with the epilogue
+        if (int rc = launch_pair<256, float>(ma, mb, p, clusters, stream)) return rc;
+        const long work = (long)M * (N / 16);
+        const dim3 rgrid((unsigned)((work + 255) / 256));
+        if (out_dtype == SB_F32) sb_launch<SB_K_REDUCE>(tc5_splitk_reduce_kernel<float>, rgrid, dim3(256), 0, stream, p);
+        else sb_launch<SB_K_REDUCE>(tc5_splitk_reduce_kernel<bf16>, rgrid, dim3(256), 0, stream, p);
+        SB_CHECK_LAUNCH("sb_gemm_tc5 (pairs, sum of the K splits)");
+        return SB_OK;
+      }
 #define SB_TC5_PAIR_LAUNCH(BN_)                                                                    \
       if (bn == BN_)                                                                               \
         return out_dtype == SB_F32 ? launch_pair<BN_, float>(ma, mb, p, clusters, stream)          \
@@ -1114,6 +1155,8 @@ static int tc5_run(const void* A, int a_dtype, const void* W, int w_dtype, int M
       SB_TC5_PAIR_LAUNCH(192)
 #undef SB_TC5_PAIR_LAUNCH
     }
+    p.k_splits = 1;
+    p.scratch = nullptr;
   }
   if (normal && N >= 192 && n_sms > 0) {
     // many rows, wide output: the persistent kernel

@@ -20,6 +20,11 @@
 //   acc_empty[a] block 0's only; the eight epilogue warps of both blocks arrive on it.
 // Every wait is bounded; a block whose wait runs out records a code, stops issuing and goes to
 // the common end, where the two blocks meet before tensor memory is given back.
+//
+// Few rows and a long inner dimension leave most pairs without a tile (256 rows of the 3,584 x
+// 18,944 product: 14 tiles for 74 pairs).  Then K is split (p.k_splits > 1): a pair's unit of work
+// is a tile's stretch of K blocks, its float32 accumulator goes to scratch [split][row][column]
+// as it is, and tc5_splitk_reduce_kernel adds the splits in order and applies the epilogue.
 #pragma once
 
 namespace {
@@ -61,8 +66,9 @@ gemm_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_a,
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_rank();
   sb_pdl_launch();
-  const int n_tiles = p.tiles_a * p.tiles_b;           // tiles of 256 x BN
-  const int n_k = (p.K + BK - 1) / BK;
+  const int S = p.k_splits;                            // K splits of a tile (1: none)
+  const int n_tiles = p.tiles_a * p.tiles_b * S;       // units of work: (tile of 256 x BN, split), splits first
+  const int n_k_all = (p.K + BK - 1) / BK, k_per = (n_k_all + S - 1) / S;
   const int first = (int)(blockIdx.x >> 1), step = (int)(gridDim.x >> 1);
 
   if (threadIdx.x == 0) {
@@ -91,10 +97,12 @@ gemm_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_a,
     const uint32_t full_of_0 = map_to_block(full0, 0);
     uint32_t it = 0;
     bool ok = true;
-    for (int tile = first; tile < n_tiles && ok; tile += step) {
+    for (int unit = first; unit < n_tiles && ok; unit += step) {
+      const int tile = unit / S, split = unit % S;
       const int tile_a = tile % p.tiles_a, tile_b = tile / p.tiles_a;
       const int a_row = tile_a * PAIR_M + (int)rank * BM, b_row = tile_b * BN + (int)rank * (BN / 2);
-      for (int kt = 0; kt < n_k; ++kt, ++it) {
+      const int k_end = min(n_k_all, (split + 1) * k_per);
+      for (int kt = split * k_per; kt < k_end; ++kt, ++it) {
         const uint32_t s = it % STAGES;
         ok = mbar_wait(empty0 + 8 * s, ((it / STAGES) & 1) ^ 1, 1);
         if (!ok) break;
@@ -114,13 +122,14 @@ gemm_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_a,
     constexpr uint32_t idesc = pair_instr_desc(BN);
     uint32_t it = 0, lt = 0;
     bool ok = true;
-    for (int tile = first; tile < n_tiles && ok; tile += step, ++lt) {
+    for (int unit = first; unit < n_tiles && ok; unit += step, ++lt) {
       const uint32_t acc = lt & 1;
       ok = mbar_wait(acc_empty0 + 8 * acc, ((lt >> 1) & 1) ^ 1, 5);   // both epilogues have drained it
       if (!ok) break;
       tc_fence_after();
       const uint32_t d_tmem = tmem_base + acc * ACC_COLS;
-      for (int kt = 0; kt < n_k; ++kt, ++it) {
+      const int k_begin = (unit % S) * k_per, k_end = min(n_k_all, k_begin + k_per);
+      for (int kt = k_begin; kt < k_end; ++kt, ++it) {
         const uint32_t s = it % STAGES;
         ok = mbar_wait(full0 + 8 * s, (it / STAGES) & 1, 3);
         if (!ok) break;
@@ -130,7 +139,7 @@ gemm_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_a,
 #pragma unroll
         for (int k = 0; k < BK / UMMA_K; ++k)
           umma_bf16_pair(d_tmem, adesc + (uint64_t)(k * UMMA_K * 2 >> 4),
-                         bdesc + (uint64_t)(k * UMMA_K * 2 >> 4), idesc, (kt > 0 || k > 0) ? 1u : 0u);
+                         bdesc + (uint64_t)(k * UMMA_K * 2 >> 4), idesc, (kt > k_begin || k > 0) ? 1u : 0u);
         umma_commit_pair(empty0 + 8 * s, 3);
       }
       if (ok) umma_commit_pair(acc_full0 + 8 * acc, 3);
@@ -143,13 +152,31 @@ gemm_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_a,
     float* stage = reinterpret_cast<float*>(smem_raw + (staging - raw)) + (warp - 2) * 32 * 33;
     const uint32_t acc_empty_of_0 = map_to_block(acc_empty0, 0);
     uint32_t lt = 0;
-    for (int tile = first; tile < n_tiles; tile += step, ++lt) {
+    for (int unit = first; unit < n_tiles; unit += step, ++lt) {
+      const int tile = unit / S, split = unit % S;
       const int tile_a = tile % p.tiles_a, tile_b = tile / p.tiles_a;
       const uint32_t acc = lt & 1;
       if (!mbar_wait(acc_full0 + 8 * acc, (lt >> 1) & 1, 4)) break;
       tc_fence_after();
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + acc * ACC_COLS;
       const int m_base = tile_a * PAIR_M + (int)rank * BM + q * 32;
+      if (S > 1) {
+        // the split's part of the sum as it is: the thread's row, 16 bytes at a time
+        const int m = m_base + lane;
+        float* dst = p.scratch + ((size_t)split * p.M + (m < p.M ? m : 0)) * p.N;
+#pragma unroll 1
+        for (int c = group; c < BN / 32; c += PAIR_EPI_GROUPS) {
+          uint32_t r[32];
+          tmem_ld32(t_row + c * 32, r);
+          const int n0 = tile_b * BN + c * 32;
+          if (m < p.M)
+#pragma unroll
+            for (int j = 0; j < 32; j += 4)
+              if (n0 + j < p.N)
+                *reinterpret_cast<float4*>(dst + n0 + j) = make_float4(
+                    __uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+        }
+      } else {
 #pragma unroll 1
       for (int c = group; c < BN / 32; c += PAIR_EPI_GROUPS) {
         uint32_t r[32];
@@ -162,6 +189,7 @@ gemm_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_a,
         tmem_ld16(t_row + (BN / 32) * 32, r);
         const int n0 = tile_b * BN + (BN / 32) * 32;
         if (n0 < p.N) store_chunk<TO, 16>(p, stage, r, m_base, n0, lane);
+      }
       }
       tc_fence_before();
       __syncwarp();
@@ -176,6 +204,49 @@ gemm_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_a,
   cluster_arrive();
   cluster_wait();
   if (warp == 1) tmem_dealloc_pair(tmem_base, 512);
+}
+
+// Adds the splits of a product whose K was split (scratch [split][row][column], float32) in
+// split order and applies the epilogue.  A thread takes 16 consecutive columns of one row (a
+// group of 8 gates and their 8 up values when the epilogue is the fused gate/up one).
+template <typename TO>
+__global__ void __launch_bounds__(256) tc5_splitk_reduce_kernel(const Tc5Params p) {
+  sb_pdl_launch();
+  sb_pdl_wait();
+  const long groups = (long)p.N / 16, idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long)p.M * groups) return;
+  const int m = (int)(idx / groups), n0 = (int)(idx % groups) * 16;
+  float v[16];
+#pragma unroll
+  for (int j = 0; j < 16; ++j) v[j] = 0.0f;
+  for (int s = 0; s < p.k_splits; ++s) {
+    const float4* src = reinterpret_cast<const float4*>(p.scratch + ((size_t)s * p.M + m) * p.N + n0);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float4 x = src[j];
+      v[4 * j] += x.x; v[4 * j + 1] += x.y; v[4 * j + 2] += x.z; v[4 * j + 3] += x.w;
+    }
+  }
+  if (p.epilogue == SB_EPI_SWIGLU) {
+    float o[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = sb_silu_out<TO>(v[j]) * v[j + 8];
+    store_row((TO*)p.out + (size_t)m * (p.N / 2) + n0 / 2, o, 8);
+    return;
+  }
+  if (p.epilogue == SB_EPI_BIAS) {
+#pragma unroll
+    for (int j = 0; j < 16; ++j)
+      v[j] += p.bias_dtype == SB_F32 ? bias_at<float>(p.bias, n0 + j) : bias_at<bf16>(p.bias, n0 + j);
+  } else if (p.epilogue == SB_EPI_RESIDUAL) {
+    const float4* res = reinterpret_cast<const float4*>(p.residual + (size_t)m * p.N + n0);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float4 x = res[j];
+      v[4 * j] += x.x; v[4 * j + 1] += x.y; v[4 * j + 2] += x.z; v[4 * j + 3] += x.w;
+    }
+  }
+  store_row((TO*)p.out + (size_t)m * p.N + n0, v, 16);
 }
 
 }  // namespace

@@ -199,6 +199,26 @@ def test_product_on_pairs_of_sms(M, N, K, width):
         assert torch.equal(a, b)
 
 
+@pytest.mark.parametrize("M,N,K", [(200, 528, 2048), (300, 400, 4096), (129, 3584, 1032), (512, 1040, 1200)])
+def test_product_with_few_rows_splits_k_over_the_pairs(M, N, K):
+    """Few row tiles and a long inner dimension: the product on pairs of SMs shares every tile's K
+    blocks out over the pairs that would have no tile (four, eight, two and two splits here),
+    writes the partial sums to scratch and adds them in split order with the epilogue.  Every
+    epilogue against the float64 product; a last split that is shorter than the others, rows that
+    end in the first block's half of a tile and a last tile that is partly outside the matrix."""
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    ops.set_tc5_pairs(1)
+    try:
+        assert int(ops.lib().sb_gemm_tc5_scratch_bytes(M, N, K, sms)) > 0, "these sizes should split K"
+        split = _every_epilogue(M, N, K)
+        ops.set_tc5_pairs(0)
+        whole = _every_epilogue(M, N, K)
+    finally:
+        ops.set_tc5_pairs(-1)
+    for a, b in zip(split, whole):                     # another order of the same sum
+        assert pm.rel_err(a.float().cpu(), b.float().cpu()) < (1e-5 if a.dtype == torch.float32 else 5e-3)
+
+
 @pytest.mark.parametrize("kernel", ["plain", "skinny", "tiled", "tc5"])
 def test_linear_rows_do_not_depend_on_the_batch(kernel):
     a, w = rnd(40, 256, dtype=torch.bfloat16), rnd(88, 256, dtype=torch.bfloat16, seed=1)
