@@ -956,6 +956,14 @@ int pair_bn(int M, int N, int clusters) {
 }  // namespace
 
 namespace {
+int pair_splits(int M, int N, int K, int clusters);
+// Whether the many-rows product runs on pairs of SMs: from 129 rows on, and from 65 rows on when
+// it would split K there (one row tile either way, but the pairs share a tile's K blocks out,
+// while one block per tile would leave most SMs without work).
+bool pair_form(int M, int N, int K, int n_sms) {
+  if (N < 192 || n_sms <= 1 || !pair_enabled()) return false;
+  return M > BM || (M > 64 && pair_splits(M, N, K, n_sms / 2) > 1);
+}
 // K splits of the pair kernel.  When even 256-column tiles leave at least half of the pairs of
 // SMs without one and the inner dimension is long enough, every tile's K blocks are shared out
 // over as many pairs as there are to spare (at most eight, at least eight K blocks each); the
@@ -1015,7 +1023,7 @@ int choose_splits(int N, int K, int n_sms) {
 // Bytes of scratch (partial tiles) the swapped form needs for these sizes; 0 when K is not split.
 extern "C" size_t sb_gemm_tc5_scratch_bytes(int M, int N, int K, int n_sms) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
-  if (M > BM && N >= 192 && n_sms > 1 && pair_enabled()) {
+  if (M > 64 && pair_form(M, N, K, n_sms)) {
     // the many-rows form on pairs of SMs, when it splits K: [split][row][column]
     const int splits = pair_splits(M, N, K, n_sms / 2);
     return splits > 1 ? (size_t)splits * M * N * sizeof(float) : 0;
@@ -1114,7 +1122,7 @@ static int tc5_run(const void* A, int a_dtype, const void* W, int w_dtype, int M
   // form: 0 picks by the number of rows, 1 forces the normal form, 2 the swapped form
   const bool normal = form == 1 || (form == 0 && M > 64);
   if (form == 2 && M > 64) SB_FAIL(SB_ERR_UNSUPPORTED, "sb_gemm_tc5: the swapped form takes at most 64 rows");
-  if (normal && N >= 192 && n_sms > 1 && M > BM && pair_enabled()) {
+  if (normal && M > 64 && pair_form(M, N, K, n_sms)) {
     // at least two row tiles, wide output: the persistent kernel on pairs of SMs
     int splits = p.rowwise ? pair_splits(M, N, K, n_sms / 2) : 1;
     if (splits > 1 && (!scratch || scratch_bytes < (size_t)splits * M * N * sizeof(float) || ((uintptr_t)scratch & 255)))

@@ -43,17 +43,28 @@ def _code(dtype: torch.dtype) -> int:
 
 
 def _ptr(t):
+    """The device address of a tensor as the typed entry points take it (an int; None is a null
+    pointer).  A step makes a few thousand of these, so no ctypes object is made here."""
     if t is None:
-        return ctypes.c_void_p(0)
+        return None
     if not t.is_cuda:
         raise KernelError("kernels take CUDA tensors only; there is no CPU path")
     if not t.is_contiguous():
         raise KernelError("kernels take contiguous tensors")
-    return ctypes.c_void_p(t.data_ptr())
+    return t.data_ptr()
+
+
+# torch.cuda.current_stream() resolves the device, builds a Stream object and costs several
+# microseconds; a prompt step asks for the stream some four hundred times.  The raw handle of
+# the current device's current stream is one call where torch has it.
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_raw_device = getattr(torch._C, "_cuda_getDevice", None)
 
 
 def _stream():
-    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    if _raw_stream is not None and _raw_device is not None:
+        return _raw_stream(_raw_device())
+    return torch.cuda.current_stream().cuda_stream
 
 
 LAUNCHES = 0          # kernels launched through this module so far (a running count)
@@ -275,10 +286,10 @@ def qkv_rope_store(h: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, 
                           page_off, page_ids, page_size, cache, q_out)
     assert inv_freq.dtype == torch.float32 and inv_freq.numel() >= rotary_dim // 2
     rope = RopeStore(n_q_heads, n_kv_heads, head_dim, rotary_dim, inv_freq.data_ptr(),
-                     _i32(row_seq, "row_seq").value, _i32(row_pos, "row_pos").value,
-                     _i32(page_off, "page_off").value if has_kv else None,
-                     _i32(page_ids, "page_ids").value if has_kv else None, page_size,
-                     cache.data_ptr() if has_kv else None, _ptr(q_out).value)
+                     _i32(row_seq, "row_seq"), _i32(row_pos, "row_pos"),
+                     _i32(page_off, "page_off") if has_kv else None,
+                     _i32(page_ids, "page_ids") if has_kv else None, page_size,
+                     cache.data_ptr() if has_kv else None, _ptr(q_out))
     extras = LinearExtras()
     extras.rope = ctypes.pointer(rope)
     ws = _tc5_workspace(M, N, K, h.device)
@@ -335,15 +346,17 @@ _tc5_buffers: dict = {}          # device -> list of workspaces (never freed:
 
 
 def _sm_count(device) -> int:
-    key = torch.device(device).index or 0
-    if key not in _sm_counts:
-        _sm_counts[key] = torch.cuda.get_device_properties(key).multi_processor_count
-    return _sm_counts[key]
+    n = _sm_counts.get(device)
+    if n is None:
+        key = torch.device(device).index or 0
+        n = _sm_counts[device] = torch.cuda.get_device_properties(key).multi_processor_count
+    return n
 
 
 def _tc5_workspace(M: int, N: int, K: int, device):
-    """Workspace of the split-K decode product: the partial tiles.  One buffer per device
-    serves every call on the stream; it only grows."""
+    """Workspace of a tcgen05 product that splits K (the decode form, and the many-rows form when
+    it has few row tiles): the partial sums.  One buffer per device serves every call on the
+    stream; it only grows."""
     l = lib()
     need = int(l.sb_gemm_tc5_scratch_bytes(M, N, K, _sm_count(device)))
     if need == 0:

@@ -199,11 +199,12 @@ def test_product_on_pairs_of_sms(M, N, K, width):
         assert torch.equal(a, b)
 
 
-@pytest.mark.parametrize("M,N,K", [(200, 528, 2048), (300, 400, 4096), (129, 3584, 1032), (512, 1040, 1200)])
+@pytest.mark.parametrize("M,N,K", [(200, 528, 2048), (300, 400, 4096), (129, 3584, 1032), (512, 1040, 1200), (100, 1040, 2048)])
 def test_product_with_few_rows_splits_k_over_the_pairs(M, N, K):
     """Few row tiles and a long inner dimension: the product on pairs of SMs shares every tile's K
-    blocks out over the pairs that would have no tile (four, eight, two and two splits here),
-    writes the partial sums to scratch and adds them in split order with the epilogue.  Every
+    blocks out over the pairs that would have no tile (four, eight, two, two and four splits here),
+    writes the partial sums to scratch and adds them in split order with the epilogue (also at 65 to
+    128 rows, which otherwise run one block per tile).  Every
     epilogue against the float64 product; a last split that is shorter than the others, rows that
     end in the first block's half of a tile and a last tile that is partly outside the matrix."""
     sms = torch.cuda.get_device_properties(0).multi_processor_count
